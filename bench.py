@@ -11,9 +11,12 @@ is all-gathered over NCCL.
 Prints ONE JSON line (rank 0). `value` = selected-block FLOPs (14 * D * pairs) / step time, inputs resident
 in HBM; `e2e` = the same through moba_attn_varlen_host with host (pinned) tensors in and out, the copies inside
 the timed region (head groups pipelined: copy engines and kernels overlap);
-`roofline` = the dominant kernel group against the measured dense bf16 peak; `cpu_baseline` = the numpy
-oracle (a port of the reference's moba_naive semantics) on this box's host cores, bounded sample.
-`--impl reference` times that CPU port alone, with all host threads, on the same metric and unit.
+`roofline` = the dominant kernel group against the measured dense bf16 peak; `cpu_baseline` = the reference's own
+moba_attn_varlen_naive (installed unmodified under baseline/_ref by baseline/install_reference.sh; pure torch) on
+this box's host cores over a bounded sample of the workload -- the numpy port in oracle/ only if that install is
+missing, and the line says which (`kind`). `--impl reference` times that CPU function alone, with all host threads,
+on the same metric and unit. `checksums` = CRC32 of the bf16 bits of a few heads of out (after the head re-layout of
+the gathered output when N > 1) and of rank 0's first head of dq / dk / dv: equal across N = 1 / 2 / 4 / 8.
 """
 import argparse
 import json
@@ -185,27 +188,58 @@ def make_inputs(cfg_id, cfg, head_lo, head_hi, device):
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
-def cpu_port_sample(cfg_id, cfg, tokens, threads):
-    """Times the numpy oracle (forward + backward) on the first `tokens` tokens of one head of the workload.
-    Returns (tflops, seconds, description)."""
+def _cpu_inputs(cfg_id, cfg, tokens):
+    """First `tokens` tokens of one head of the workload's value distribution, as fp32 numpy arrays holding bf16
+    values (seeded; the same numbers for the reference function and for the numpy port)."""
     import numpy as np
     from oracle import moba_oracle as orc
 
-    try:
-        from threadpoolctl import threadpool_limits
-    except ImportError:
-        threadpool_limits = None
     rng = np.random.RandomState(1000 * cfg_id)
     q, k, v, d_out = (orc.round_bf16(rng.randn(tokens, 1, D).astype(np.float32)) for _ in range(4))
     if cfg["off_std"] > 0:
         nb = (tokens + cfg["chunk"] - 1) // cfg["chunk"]
         off = rng.randn(nb, 1, D).astype(np.float32) * cfg["off_std"]
         k = orc.round_bf16(k + np.repeat(off, cfg["chunk"], axis=0)[:tokens])
-    cu = [0, tokens]
+    return q, k, v, d_out
+
+
+def cpu_sample(cfg_id, cfg, tokens, threads):
+    """Times the reference's CPU implementation of the path, moba_attn_varlen_naive (forward + backward through
+    torch autograd), on the first `tokens` tokens of one head of the workload; the numpy port of the same function
+    when the reference is not installed under baseline/_ref. Returns (tflops, seconds, description, kind)."""
+    from baseline import reference as ref
+
+    q, k, v, d_out = _cpu_inputs(cfg_id, cfg, tokens)
+    pairs = selected_pairs([tokens], cfg["chunk"], cfg["topk"])
+    flops = (14 if cfg["backward"] else 4) * D * pairs
+    what = (f"fwd{'+bwd' if cfg['backward'] else ''}, first {tokens} tokens of 1 head of the workload "
+            f"(chunk {cfg['chunk']}, top-k {cfg['topk']}), {threads} threads")
+    if ref.available():
+        import torch
+
+        naive = ref.load_naive()
+        torch.set_num_threads(threads)
+        tq, tk, tv, tdo = (torch.from_numpy(x).to(torch.bfloat16) for x in (q, k, v, d_out))
+        if cfg["backward"]:
+            tq.requires_grad_(), tk.requires_grad_(), tv.requires_grad_()
+        cu = torch.tensor([0, tokens], dtype=torch.int32)
+        t0 = time.perf_counter()
+        out = naive(tq, tk, tv, cu, tokens, cfg["chunk"], cfg["topk"])
+        if cfg["backward"]:
+            out.backward(tdo)
+        secs = time.perf_counter() - t0
+        return flops / secs / 1e12, secs, "reference moba_attn_varlen_naive (torch, fp32 math on bf16 inputs) " + what, "reference"
+
+    from oracle import moba_oracle as orc
+
+    try:
+        from threadpoolctl import threadpool_limits
+    except ImportError:
+        threadpool_limits = None
 
     def run():
         t0 = time.perf_counter()
-        orc.moba_attn_varlen_oracle(q, k, v, cu, tokens, cfg["chunk"], cfg["topk"], "bf16",
+        orc.moba_attn_varlen_oracle(q, k, v, [0, tokens], tokens, cfg["chunk"], cfg["topk"], "bf16",
                                     d_out=d_out if cfg["backward"] else None)
         return time.perf_counter() - t0
 
@@ -214,11 +248,13 @@ def cpu_port_sample(cfg_id, cfg, tokens, threads):
             secs = run()
     else:
         secs = run()
-    pairs = selected_pairs([tokens], cfg["chunk"], cfg["topk"])
-    flops = (14 if cfg["backward"] else 4) * D * pairs
-    desc = (f"numpy oracle fwd{'+bwd' if cfg['backward'] else ''}, first {tokens} tokens of 1 head of the workload "
-            f"(chunk {cfg['chunk']}, top-k {cfg['topk']}), {threads} threads")
-    return flops / secs / 1e12, secs, desc
+    return flops / secs / 1e12, secs, "numpy port of moba_attn_varlen_naive (baseline/_ref not installed) " + what, "port"
+
+
+def cpu_sample_tokens(cfg):
+    """Bounded sample: the dense reference function needs O(tokens^2) fp32 per head; 16384 tokens are ~10 s of work
+    on 16 host threads."""
+    return min(16384, sum(cfg["lens"]) if len(cfg["lens"]) == 1 else max(cfg["lens"]))
 
 
 def run_reference_arm(args, cfg_id, cfg):
@@ -226,26 +262,27 @@ def run_reference_arm(args, cfg_id, cfg):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    tokens = 4 * cfg["chunk"] if cfg["chunk"] * 4 <= sum(cfg["lens"]) else sum(cfg["lens"])
+    tokens = cpu_sample_tokens(cfg)
     for _ in range(args.warmup):
-        cpu_port_sample(cfg_id, cfg, min(tokens, 2 * cfg["chunk"]), threads)
+        cpu_sample(cfg_id, cfg, min(tokens, 4096), threads)
     vals, secs = [], []
     for _ in range(args.steps):
-        tf, s, desc = cpu_port_sample(cfg_id, cfg, tokens, threads)
+        tf, s_, desc, kind = cpu_sample(cfg_id, cfg, tokens, threads)
         vals.append(tf)
-        secs.append(s)
+        secs.append(s_)
     value = sum(vals) / len(vals)
     line = {
         "impl": "reference", "metric": "moba_layer_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * sum(secs) / len(secs), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(cfg_id, cfg, args.gpus),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference is pure Python on flash-attn kernels and has no CPU implementation of its own; "
-                "this arm times the numpy port of its moba_naive semantics (oracle/) on the host cores",
+        "note": "the reference's GPU path needs flash-attn kernels; this arm times its own CPU implementation "
+                "(moba_naive) on the host cores over a bounded sample: each step is the sample named in "
+                "cpu_baseline.sample, not the whole workload",
     }
     emit(line)
 
@@ -400,6 +437,27 @@ def run_ours(args, cfg_id, cfg):
                    d2h=(4 if cfg["backward"] else 1) * nbytes)
     check_kernel_status(dev)
 
+    # ---- checksums (outside every timed region): equal bits at every N ---------------------------------
+    import zlib
+
+    from moba_b200 import head_parallel
+
+    def head_crc(t, h):
+        return zlib.crc32(t[:, h].contiguous().view(torch.int16).cpu().numpy().tobytes())
+
+    last = step()
+    full = head_parallel.gather_heads(last.detach()) if world > 1 else last.detach()      # [S, H, D], heads in order
+    checksums = {f"out_h{h}": head_crc(full, h) for h in sorted({0, H // 2 - 1 if H > 1 else 0, H - 1})}
+    if cfg["backward"]:
+        checksums.update(dq_h0=head_crc(q.grad, 0), dk_h0=head_crc(k.grad, 0), dv_h0=head_crc(v.grad, 0))
+    del full, last
+
+    secondary = None
+    if args.config == 3 and not args.no_secondary:
+        q = k = v = d_out = out_all = None
+        torch.cuda.empty_cache()
+        secondary = measure_prefill_1m(world, rank, dev)
+
     if rank == 0:
         peaks = read_peaks()
         pairs = selected_pairs(cfg["lens"], cfg["chunk"], cfg["topk"]) * H
@@ -429,8 +487,8 @@ def run_ours(args, cfg_id, cfg):
         if args.no_cpu_baseline:
             cpu = None
         else:
-            tf, secs, desc = cpu_port_sample(cfg_id, cfg, min(8 * cfg["chunk"], S), threads)
-            cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc,
+            tf, secs, desc, kind = cpu_sample(cfg_id, cfg, cpu_sample_tokens(cfg), threads)
+            cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": desc,
                    "seconds": secs}
         line = {
             "metric": "moba_layer_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -440,13 +498,74 @@ def run_ours(args, cfg_id, cfg):
             "frac_of_bf16_peak": value / (world * peaks["bf16_tflops_sustained"]),
             "kernel_ms": kernel_ms, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "gpu_launches": len(records) and args.steps * launches_per_step(cfg, world),
+            "checksums": checksums,
         }
+        if world > 1:
+            line["config"]["timed_gather_layout"] = ("rank-major [N, S, H/N, D] as the collective lands it; the "
+                                                     "[S, H, D] re-layout is applied for `checksums` only")
+        if secondary:
+            line["secondary"] = secondary
         if e2e:
             line["e2e"] = {"value": flops / (e2e["ms"] * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e["ms"],
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_prefill_1m(world, rank, dev, steps=3, warmup=1):
+    """The 1M-token forward-only configuration (config 5: 1048576 tokens, 32 heads from 8 KV heads, chunk 4096,
+    top-k 12) beside the headline line, so that its curve over N is visible too: every rank runs its 32 / N heads in
+    groups of at most 4 and all-gathers each group's output (NCCL) while the next group computes."""
+    import torch
+    import torch.distributed as dist
+
+    from moba_b200.moba_efficient import check_kernel_status, moba_attn_varlen
+
+    cfg = CONFIGS[5]
+    S, H = sum(cfg["lens"]), cfg["heads"]
+    hl = H // world
+    q, k, v, _ = make_inputs(5, cfg, rank * hl, (rank + 1) * hl, dev)
+    cu = torch.tensor([0, S], dtype=torch.int32, device=dev)
+    gw = min(4, hl)
+    groups = [(a, min(a + gw, hl)) for a in range(0, hl, gw)]
+    gathered = [torch.empty((world * S, b - a, D), dtype=torch.bfloat16, device=dev) for a, b in groups[:2]] if world > 1 else None
+
+    def step():
+        works = []
+        for g, (a, b) in enumerate(groups):
+            with torch.no_grad():
+                o = moba_attn_varlen(q[:, a:b], k[:, a:b], v[:, a:b], cu, S, cfg["chunk"], cfg["topk"])
+            if world > 1:
+                if len(works) >= 2:
+                    works.pop(0).wait()
+                works.append(dist.all_gather_into_tensor(gathered[g % 2], o, async_op=True))
+        for w in works:
+            w.wait()
+
+    for _ in range(warmup):
+        step()
+    check_kernel_status(dev)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    check_kernel_status(dev)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    flops = 4 * D * selected_pairs(cfg["lens"], cfg["chunk"], cfg["topk"]) * H
+    return {"metric": "moba_layer_fwd_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "ms_per_step": ms, "steps": steps, "warmup": warmup, "n_gpus": world, "scaling": "strong",
+            "config": workload_config(5, cfg, world)}
 
 
 def run_decode(args, cfg_id, cfg):
@@ -510,6 +629,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--head-groups", type=int, default=8, help="head slices pipelined in the end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the 1M-token forward-only line (config 3 runs)")
     args = ap.parse_args()
     claim_stdout()
     cfg = CONFIGS[args.config]

@@ -150,10 +150,13 @@ int moba_gate_topk(const void* q, int32_t dtype, int32_t H, int64_t stride_s, in
  *   work_off   [n_chunks*H + 1] int32: prefix sum of ceil(len/128) = first gathered tile of every expert
  *   list_tok   [R*H] int32: token of every row
  *   row_of     [S, H, kk] int32: row that slot j of (token, head) occupies, -1 if the slot is empty
+ *   status     device status word or NULL: a chunk id in sel that is not a candidate of its query (only a sel
+ *              buffer that moba_gate_topk did not write can hold one) is skipped like an empty slot and sets
+ *              the word to 2 (bad index)
  */
 int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_dev, const int32_t* sel,
                      int32_t* tile_cnt, int32_t* list_off, int32_t* work_off, int32_t* list_tok,
-                     int32_t* row_of, int32_t device, void* stream);
+                     int32_t* row_of, int32_t* status, int32_t device, void* stream);
 
 /*
  * Forward attention tiles (tcgen05 / TMEM, TMA-fed K and V, online softmax). Replaces the two
@@ -283,11 +286,13 @@ int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_rows, const
                               const void* b, float* c, int32_t dtype, int32_t* status, int32_t device,
                               void* stream);
 
-/* Diagnostic: n_ctas CTAs each issue iters groups of eight UMMA instructions of one shape (mode 0..10, see
- * csrc/selftest.cu) and write the elapsed SM clocks to cycles[n_ctas]. Modes 11-15 time what the issuing warp does
- * after tcgen05.commit and write eight slots per CTA (cycles[8 * n_ctas]). */
-int moba_selftest_mma_rate(int32_t mode, int32_t iters, int32_t n_ctas, long long* cycles, int32_t* status,
-                           int32_t device, void* stream);
+/*
+ * Failure-path self test (not on any product path): n_ctas CTAs allocate tensor memory and wait on an mbarrier that
+ * nothing arrives on, for at most limit_ns nanoseconds (1e3 .. 1e8). The waits run out, the kernel sets *status to
+ * 1, releases its tensor memory and returns; moba_check_status then reports MOBA_ERR_DEVICE and the context stays
+ * usable. This is how every bounded wait of the product kernels ends when its limit (2 s there) is reached.
+ */
+int moba_selftest_wait_timeout(int64_t limit_ns, int32_t n_ctas, int32_t* status, int32_t device, void* stream);
 
 #ifdef __cplusplus
 }

@@ -70,7 +70,7 @@ SIGNATURES = {
     "moba_pool_keys_static_max_floats": (_I64, []),
     "moba_pool_keys_static": (ctypes.c_int, [_P, _I32, _I32, _I64, _I64, _INFO, _P, _P, _I32, _P]),
     "moba_gate_topk": (ctypes.c_int, [_P, _I32, _I32, _I64, _I64, _P, _I32, _INFO, _P, _P, _P, _P, _P, _I32, _P]),
-    "moba_build_lists": (ctypes.c_int, [_I32, _INFO, _P, _P, _P, _P, _P, _P, _P, _I32, _P]),
+    "moba_build_lists": (ctypes.c_int, [_I32, _INFO, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _P]),
     "moba_attn_fwd": (ctypes.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P,
                                      _P, _I32, _P, _I32, _P]),
     "moba_merge_fwd": (ctypes.c_int, [_P, _P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),
@@ -89,7 +89,7 @@ SIGNATURES = {
     "moba_check_status": (ctypes.c_int, [_P, _I32, _P]),
     "moba_selftest_umma": (ctypes.c_int, [_I32, _P, _P, _P, _I32, _P, _I32, _P]),
     "moba_selftest_umma_gather": (ctypes.c_int, [_I32, _P, _I32, _P, _P, _P, _I32, _P, _I32, _P]),
-    "moba_selftest_mma_rate": (ctypes.c_int, [_I32, _I32, _I32, _P, _P, _I32, _P]),
+    "moba_selftest_wait_timeout": (ctypes.c_int, [_I64, _I32, _P, _I32, _P]),
 }
 
 

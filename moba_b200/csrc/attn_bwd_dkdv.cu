@@ -32,16 +32,6 @@ namespace {
 constexpr int kDkdvThreads = 384;
 constexpr int kMmaWarp0 = 8, kLoaderWarp0 = 10;      // 8, 9: MMA issue for the even / odd half tiles; 10, 11: loaders
 
-// Optional timeline of one CTA (compile with -DMOBA_TRACE): (tag, half tile, SM clock) triples.
-#ifdef MOBA_TRACE
-__device__ long long g_dkdv_trace[10 * 512];
-#define MOBA_TR(tag, g)                                                                   \
-  do {                                                                                    \
-    if (blockIdx.x == 3 && blockIdx.y == 0 && (g) < 512) g_dkdv_trace[(tag) * 512 + (g)] = clock64(); \
-  } while (0)
-#else
-#define MOBA_TR(tag, g) do {} while (0)
-#endif
 constexpr int kStages = 4;
 
 struct __align__(1024) DkdvSmem {
@@ -202,7 +192,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         go = __shfl_sync(0xffffffffu, go, 0);
       }
       if (!go) break;
-      if (lane == 0) MOBA_TR(7, g);
       *reinterpret_cast<uint4*>(sm.lse_b[st] + nosw_offset(lane, 0)) = make_uint4(xl_a, 0, 0, 0);
       *reinterpret_cast<uint4*>(sm.lse_b[st] + nosw_offset(lane + 32, 0)) = make_uint4(xl_b, 0, 0, 0);
       *reinterpret_cast<uint4*>(sm.dlt_b[st] + nosw_offset(lane, 0)) = make_uint4(xd_a, 0, 0, 0);
@@ -223,7 +212,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           tma_load_3d(do_dst, &map_dog, &sm.bar_q_full[st], 0, 0, row0);
           tma_load_3d(do_dst + 8192, &map_dog, &sm.bar_q_full[st], 64, 0, row0);
         }
-        MOBA_TR(8, g);
       }
     }
   } else if (warp >= kMmaWarp0) {
@@ -311,13 +299,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             {g > 0 ? &sm.bar_acc_done : &sm.bar_p_ready[mb], static_cast<uint32_t>(g > 0 ? (g - 1) & 1 : (g >> 1) & 1)}};
         ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
         if (!ok) break;
-        if (lane == 0) MOBA_TR(1, g);
         tc_fence_after_sync();
         issue_acc(g);
-        if (lane == 0) MOBA_TR(2, g);
         if (more) issue_sdp(g + 2);
         if (g == n_half - 1) umma_commit_w(leader, &sm.bar_all_done);     // follows every other product
-        if (lane == 0) MOBA_TR(4, g);
       }
       if (!ok) __nanosleep(1000000);
     }
@@ -334,7 +319,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       const int st = g & (kStages - 1), h = g & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_q_full[st], (g >> 2) & 1, wctx) && mbar_wait(&sm.bar_s_ready[h], (g >> 1) & 1, wctx));
       if (!ok) break;
-      if (tid == 0) MOBA_TR(5, g);
       tc_fence_after_sync();
       // the first own-chunk tile of every head's segment is the diagonal one: key <= query
       const bool diag = n_self > 0 && g - sm.seg_start[seg] < 2;
@@ -378,7 +362,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sm.bar_p_ready[h]);
-      if (tid == 0) MOBA_TR(6, g);
     }
     if (n_half == 0) {
       // no query attends these keys (list part only, empty list): the gradients are zero
@@ -406,14 +389,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 }  // namespace
 }  // namespace moba
 
-#ifdef MOBA_TRACE
-// Debug builds only: copies the recorded timeline (10 tags x 512 half tiles of SM clocks) to the host.
-extern "C" int moba_debug_dkdv_trace(long long* out, int max_events) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, moba::g_dkdv_trace, sizeof(long long) * 10 * 512);
-  return 10 * 512;
-}
-#endif
 
 extern "C" int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype,
                                   int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
@@ -427,7 +402,7 @@ extern "C" int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, c
   if (rc) return rc;
   MOBA_REQUIRE(dk && dv, MOBA_ERR_ARG, "null pointer argument");
   if (info->kk > 0 && (parts & 2)) MOBA_REQUIRE(list_off, MOBA_ERR_ARG, "null list buffers");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   if (info->n_qtiles == 0) return 0;
   CUtensorMap mk, mv;
   BwdArgs a;

@@ -32,16 +32,6 @@ constexpr int kComputeWarps = 16;
 constexpr int kWarpS = 16, kWarpDp = 17, kWarpDq = 18, kTmaWarp = 19;
 constexpr int kKSlots = 3, kVSlots = 2;
 
-// Optional timeline of one list-tile CTA (compile with -DMOBA_TRACE): SM clock per (tag, half tile).
-#ifdef MOBA_TRACE
-__device__ long long g_dq_trace[12 * 128];
-#define MOBA_TR(tag, g)                                                                              \
-  do {                                                                                               \
-    if (kGathered && blockIdx.x == 5000 && (g) < 128) g_dq_trace[(tag) * 128 + (g)] = clock64();      \
-  } while (0)
-#else
-#define MOBA_TR(tag, g) do {} while (0)
-#endif
 
 struct __align__(1024) DqSmem {
   uint8_t q[2][16384];              // [d half][128 rows x 64], 128-byte swizzle
@@ -65,7 +55,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   WaitCtx wctx{&sm.abort_flag, a.status};
 
-  if (tid == 0) MOBA_TR(10, 0);
   // ---- prologue: work item (warp 0), barriers (warp 1) and tensor memory (warp A0) in parallel --------------
   if (warp == 0) {
     int chunk = 0, head = 0, first = 0, n_rows = 0, key0 = 0, nkeys = 0, active = 1;
@@ -152,7 +141,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (warp == kWarpS) tmem_dealloc(sm.tmem_base, 512);
     return;
   }
-  if (tid == 0) MOBA_TR(10, 1);
   const int head = sm.work[1], first = sm.work[2], n_rows = sm.work[3], key0 = sm.work[5], nkeys = sm.work[6];
   const int nkv = (nkeys + MOBA_TILE - 1) / MOBA_TILE;      // key tiles
   const uint32_t tmem = sm.tmem_base;
@@ -171,7 +159,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       dlt = a.delta[i] * kSoftmaxScale;
     }
   }
-  if (tid == 0) MOBA_TR(10, 3);
 
   if (warp == kTmaWarp) {
     // ================= TMA producer =================
@@ -215,7 +202,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           {j >= 2 ? &sm.bar_buf_free[b] : &sm.bar_qdo_full, static_cast<uint32_t>(j >= 2 ? ((j >> 1) - 1) & 1 : 0)}};
       ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
       if (!ok) break;
-      if (lane == 0) MOBA_TR(3, j);
       tc_fence_after_sync();
       const uint64_t k_km = k_km0 + static_cast<uint32_t>(sk) * (32768u >> 4);
 #pragma unroll
@@ -224,7 +210,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         umma_ss_w(leader, tmem + b * 128u, q_km + off, k_km + off, idesc, ks > 0);
       }
       umma_commit_w(leader, &sm.bar_s_ready[b]);
-      if (lane == 0) MOBA_TR(4, j);
     }
     if (!ok) __nanosleep(1000000);
   } else if (warp == kWarpDp) {
@@ -264,7 +249,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       const int b = j & 1, sk = j % kKSlots;
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_ds_ready[b], (j >> 1) & 1, wctx));
       if (!ok) break;
-      if (lane == 0) MOBA_TR(1, j);
       tc_fence_after_sync();
       const uint64_t k_mn = k_mn0 + static_cast<uint32_t>(sk) * (32768u >> 4);
       const uint32_t a_ds = tmem + b * 128u;
@@ -273,7 +257,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       for (int ks = 0; ks < 8; ++ks) umma_ts_w(leader, tm_dq, a_ds + ks * 8, k_mn + ((ks * 2048u) >> 4), idesc, ks > 0 ? 1u : acc);
       umma_commit_w(leader, &sm.bar_k_empty[sk]);      // S_j finished before dS_j existed
       umma_commit_w(leader, &sm.bar_buf_free[b]);
-      if (lane == 0) MOBA_TR(2, j);
     }
     // dQ is complete when this warp's products are; all others precede the last of them through the barriers
     if (ok) umma_commit_w(leader, &sm.bar_all_done);
@@ -290,7 +273,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                                 {&sm.bar_dp_ready, static_cast<uint32_t>(j & 1)}};
       ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
       if (!ok) break;
-      if (tid == 0) MOBA_TR(5, j);
       tc_fence_after_sync();
       int ncol = nkeys - j * MOBA_TILE;                            // keys of this tile that exist
       if constexpr (!kGathered) ncol = min(ncol, first + row - key0 - j * MOBA_TILE + 1);   // causal: key <= query
@@ -303,7 +285,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       // dP is in registers: the next tile's dP may overwrite the buffer
       tc_fence_before_sync();
       mbar_arrive(&sm.bar_dp_free);
-      if (tid == 0) MOBA_TR(7, j);
       uint32_t pd[16];
       if (full) {
 #pragma unroll
@@ -327,17 +308,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       }
       // the 16-bit results land on TMEM columns [0, 64) of the S buffer, which other warps of the lane quarter
       // read their fp32 inputs from: all four must have their inputs in registers first
-      if (tid == 0) MOBA_TR(8, j);
       asm volatile("bar.sync %0, 128;" ::"r"(quad_bar) : "memory");
-      if (tid == 0) MOBA_TR(9, j);
       tmem_st16(t_s + ci * 16, pd);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sm.bar_ds_ready[b]);
-      if (tid == 0) MOBA_TR(6, j);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_all_done, 0, wctx));
-    if (tid == 0) MOBA_TR(10, 4);
     // ---- epilogue: dQ rows -> global memory through shared memory, so that a warp writes whole 512-byte rows
     // (thread = row straight from TMEM writes 16 bytes per row and instruction: measured 6500 clocks per tile).
     // The K/V ring is idle by now; the staging rows are padded to 132 floats against bank conflicts.
@@ -371,21 +348,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (tid == 0) MOBA_TR(10, 5);
   if (warp == kWarpS) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
 }  // namespace moba
 
-#ifdef MOBA_TRACE
-// Debug builds only: copies the recorded timeline to the host.
-extern "C" int moba_debug_dq_trace(long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, moba::g_dq_trace, sizeof(long long) * 12 * 128);
-  return 12 * 128;
-}
-#endif
 
 extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype,
                                 int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
@@ -399,7 +367,7 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
   if (rc) return rc;
   MOBA_REQUIRE(dq || !(parts & 1), MOBA_ERR_ARG, "null pointer argument");
   if (info->kk > 0 && (parts & 2)) MOBA_REQUIRE(list_off && work_off && list_tok && part_dq, MOBA_ERR_ARG, "null list / partial buffers");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   if (info->n_qtiles == 0) return 0;
   CUtensorMap mk, mv;   // 128-key boxes
   BwdArgs a;

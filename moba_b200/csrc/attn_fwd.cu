@@ -42,16 +42,6 @@ constexpr int kMmaWarp = 8, kTmaWarp = 9;
 constexpr int kTmemCols = 256;
 constexpr float kRescaleThreshold = 8.0f;
 
-// Optional timeline of one list-tile CTA (compile with -DMOBA_TRACE): SM clock per (tag, key tile).
-#ifdef MOBA_TRACE
-__device__ long long g_fwd_trace[12 * 64];
-#define MOBA_TR(tag, j)                                                                             \
-  do {                                                                                              \
-    if (kGathered && blockIdx.x == 300 && (j) < 64) g_fwd_trace[(tag) * 64 + (j)] = clock64();      \
-  } while (0)
-#else
-#define MOBA_TR(tag, j) do {} while (0)
-#endif
 
 struct __align__(1024) FwdSmem {
   uint8_t q[2][16384];              // [128 rows x 64] sub-tiles, 128-byte swizzle (d 0..63 | d 64..127)
@@ -247,7 +237,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           {more ? &sm.bar_k_full : &sm.bar_v_full, static_cast<uint32_t>(more ? (j + 1) & 1 : j & 1)}};
       ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
       if (!ok) break;
-      if (lane == 0) MOBA_TR(1, j);
       tc_fence_after_sync();
       const uint32_t acc = j > 0;
 #pragma unroll
@@ -256,7 +245,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       umma_commit_w(leader, &sm.bar_v_empty);
       if (more) issue_s();
       else umma_commit_w(leader, &sm.bar_all_done);
-      if (lane == 0) MOBA_TR(2, j);
     }
     if (!ok) __nanosleep(1000000);   // let copies already in flight land before the CTA retires
   } else {
@@ -270,7 +258,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     for (int j = 0; j < nkv; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_s_ready, j & 1, wctx));
       if (!ok) break;
-      if (tid == 0) MOBA_TR(5, j);
       tc_fence_after_sync();
       const bool last = j == nkv - 1;
       int ncol = nkeys - j * MOBA_TILE;                       // keys of this tile that exist
@@ -318,7 +305,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         }
       };
       probabilities(true);
-      if (tid == 0) MOBA_TR(8, j);
       sm.xchg[ch][row] = mx;
       // also orders the in-place write of P below after every S load of the row's two threads
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
@@ -349,12 +335,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       }
       l_sum += ls0 + ls1;
-      if (tid == 0) MOBA_TR(9, j);
       tmem_st32(t_s + ch * 32, pk);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sm.bar_p_ready);
-      if (tid == 0) MOBA_TR(6, j);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_all_done, 0, wctx));
     // ---- epilogue: O / l rows -> global memory through shared memory, so that a warp writes whole 256-byte rows
@@ -411,18 +395,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
-#ifdef MOBA_TRACE
-}  // namespace
-}  // namespace moba
-// Debug builds only: copies the recorded timeline to the host.
-extern "C" int moba_debug_fwd_trace(long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, moba::g_fwd_trace, sizeof(long long) * 12 * 64);
-  return 12 * 64;
-}
-namespace moba {
-namespace {
-#endif
 
 template <bool kBf16>
 int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mv, FwdArgs args, const FwdArgs& gargs,
@@ -464,7 +436,7 @@ extern "C" int moba_attn_fwd(const void* q, const void* k, const void* v, int32_
                "attention kernels take bf16 or f16 tensors (dtype=%d)", dtype);
   if (info->kk > 0 && (parts & 2))
     MOBA_REQUIRE(list_off && work_off && list_tok && part_o && part_lse, MOBA_ERR_ARG, "null list / partial buffers");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   if (info->n_qtiles == 0) return 0;
   CUtensorMap mk, mv;
   FwdArgs a;

@@ -25,6 +25,28 @@ int set_error(int code, const char* fmt, ...);
     }                                                                                          \
   } while (0)
 
+// Makes `device` current for the rest of the calling function and restores the caller's device on every return
+// path: the library shares the thread's CUDA context with its caller (torch), which must not find its current
+// device changed by a call that was handed tensors of another GPU.
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t set(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev == device) return cudaSuccess;
+    e = cudaSetDevice(device);
+    changed = e == cudaSuccess;
+    return e;
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+#define MOBA_SET_DEVICE(device)  \
+  moba::DeviceGuard _moba_device_guard; \
+  MOBA_CUDA_OK(_moba_device_guard.set(device))
+
 #define MOBA_REQUIRE(cond, code, ...)                     \
   do {                                                    \
     if (!(cond)) return moba::set_error((code), __VA_ARGS__); \

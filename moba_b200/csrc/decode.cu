@@ -394,7 +394,7 @@ extern "C" int moba_decode_attn(const void* q, const void* k, const void* v, int
   a.status = status;
   const int64_t n_ctas = n_bh * a.row_blocks * a.splits;
   MOBA_REQUIRE(n_ctas < (1ll << 31) && n_bh < (1ll << 31), MOBA_ERR_LIMIT, "too many (batch, head, row block, range) items");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   // K / V as [batch * kv_heads] "heads" of kv_len tokens: one 3-D tensor map each (64-key boxes)
   CUtensorMap mk, mv;
   int rc = make_tensor_map_shd(&mk, k, dtype, kv_len, static_cast<int32_t>(n_bh), kv_stride_l, kv_stride_h, kKeyTile);

@@ -237,7 +237,7 @@ offsets_kernel(int E, int32_t* __restrict__ list_off, int32_t* __restrict__ work
 __global__ void __launch_bounds__(128)
 fill_lists_kernel(int H, PlanDev plan, const int32_t* __restrict__ sel, const int32_t* __restrict__ tile_cnt,
                   const int32_t* __restrict__ list_off, int32_t* __restrict__ list_tok,
-                  int32_t* __restrict__ row_of) {
+                  int32_t* __restrict__ row_of, int* status) {
   extern __shared__ __align__(16) uint8_t fill_smem[];
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(fill_smem);
   const int tile = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -256,10 +256,13 @@ fill_lists_kernel(int H, PlanDev plan, const int32_t* __restrict__ sel, const in
   }
   for (int i = tid; i < ncand * 4; i += 128) bitmap[i] = 0u;
   __syncthreads();
+  // a chunk id outside the candidates of this tile (a caller's buffer that the gate did not write) is treated
+  // as an empty slot and reported through the status word; it must not index the bitmap or the lists
   if (valid)
     for (int j = 0; j < kk; ++j) {
       const int g = sel[slot0 + j];
-      if (g >= 0) atomicOr(&bitmap[(g - c0) * 4 + warp], 1u << lane);
+      if (g >= c0 && g < chunk) atomicOr(&bitmap[(g - c0) * 4 + warp], 1u << lane);
+      else if (g >= 0 && status) atomicCAS(status, 0, 2);
     }
   __syncthreads();
   if (!valid) return;
@@ -268,7 +271,7 @@ fill_lists_kernel(int H, PlanDev plan, const int32_t* __restrict__ sel, const in
   for (int j = 0; j < kk; ++j) {
     const int g = sel[slot0 + j];
     int r = -1;
-    if (g >= 0) {
+    if (g >= c0 && g < chunk) {
       const int lc = g - c0;
       int rank = __popc(bitmap[lc * 4 + warp] & lt);
       for (int w = 0; w < warp; ++w) rank += __popc(bitmap[lc * 4 + w]);
@@ -317,7 +320,7 @@ extern "C" int moba_gate_topk(const void* q, int32_t dtype, int32_t H, int64_t s
   MOBA_REQUIRE(info->max_cand <= 11000, MOBA_ERR_LIMIT,
                "a sequence has %d chunks; at most 11001 are supported", info->max_cand + 1);
   MOBA_REQUIRE(info->cand_per_head * H < (1ll << 31), MOBA_ERR_LIMIT, "candidate table exceeds 2^31 entries");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   if (info->n_qtiles == 0) return 0;
   const PlanDev plan = make_plan_dev(info, meta_dev);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -338,7 +341,8 @@ extern "C" int moba_gate_topk(const void* q, int32_t dtype, int32_t H, int64_t s
 
 extern "C" int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_dev,
                                 const int32_t* sel, int32_t* tile_cnt, int32_t* list_off, int32_t* work_off,
-                                int32_t* list_tok, int32_t* row_of, int32_t device, void* stream) {
+                                int32_t* list_tok, int32_t* row_of, int32_t* status, int32_t device,
+                                void* stream) {
   using namespace moba;
   MOBA_REQUIRE(info && meta_dev && sel && tile_cnt && list_off && work_off && list_tok && row_of, MOBA_ERR_ARG,
                "null pointer argument");
@@ -346,7 +350,7 @@ extern "C" int moba_build_lists(int32_t H, const moba_plan_info* info, const int
   MOBA_REQUIRE(info->kk >= 1, MOBA_ERR_ARG, "no selection slots (kk=0)");
   MOBA_REQUIRE(info->rows_per_head * H < (1ll << 31), MOBA_ERR_LIMIT, "row space exceeds 2^31");
   MOBA_REQUIRE(static_cast<int64_t>(info->n_chunks) * H < (1ll << 30), MOBA_ERR_LIMIT, "too many experts");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   if (info->n_qtiles == 0) return 0;
   const PlanDev plan = make_plan_dev(info, meta_dev);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -358,7 +362,7 @@ extern "C" int moba_build_lists(int32_t H, const moba_plan_info* info, const int
   const size_t smem = static_cast<size_t>(info->max_cand > 0 ? info->max_cand : 1) * 16;
   MOBA_CUDA_OK(cudaFuncSetAttribute(fill_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(plan.n_qtiles, H);
-  fill_lists_kernel<<<grid, 128, smem, st>>>(H, plan, sel, tile_cnt, list_off, list_tok, row_of);
+  fill_lists_kernel<<<grid, 128, smem, st>>>(H, plan, sel, tile_cnt, list_off, list_tok, row_of, status);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -178,13 +178,15 @@ gate_topk_umma_kernel(const __grid_constant__ CUtensorMap map_q, int H, const fl
     if (!ok) break;
   }
 
-  if (ok && valid) {
+  if (valid) {
+    // A wait that ran out leaves the scores unknown: the tile's queries then select nothing (the status word
+    // carries the error), so that the list kernels downstream never see an uninitialised chunk id.
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) {
       if (j < kk) {
-        const int lc = bidx[j];
+        const int lc = ok ? bidx[j] : -1;
         sel[slot0 + j] = lc >= 0 ? c0 + lc : -1;
-        if (sel_score) sel_score[slot0 + j] = best[j];
+        if (sel_score) sel_score[slot0 + j] = ok ? best[j] : -INFINITY;
         if (lc >= 0) atomicOr(&bitmap[lc * 4 + warp], 1u << lane);
       }
     }

@@ -11,7 +11,7 @@ extern "C" int moba_memcpy_2d(void* dst, int64_t dst_pitch, const void* src, int
                "bad 2-D copy geometry (width %lld, rows %lld, pitches %lld / %lld)", (long long)width_bytes,
                (long long)rows, (long long)dst_pitch, (long long)src_pitch);
   if (rows == 0) return 0;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   MOBA_CUDA_OK(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch),
                                  static_cast<size_t>(width_bytes), static_cast<size_t>(rows),
                                  to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,

@@ -182,7 +182,7 @@ extern "C" int moba_merge_fwd(void* out, float* lse, int32_t dtype, int32_t H, c
   MOBA_REQUIRE(H >= 1, MOBA_ERR_ARG, "H=%d must be >= 1", H);
   MOBA_REQUIRE(info->kk >= 1 && info->kk <= 32, MOBA_ERR_ARG, "kk=%d outside [1, 32]", info->kk);
   if (int rc = check16(dtype)) return rc;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const int64_t n = static_cast<int64_t>(info->total_tokens) * H;
   if (n == 0) return 0;
   const unsigned grid = static_cast<unsigned>((n + 7) / 8);
@@ -203,7 +203,7 @@ extern "C" int moba_bwd_delta(const void* out, const void* d_out, int32_t dtype,
   MOBA_REQUIRE(out && d_out && delta, MOBA_ERR_ARG, "null pointer argument");
   MOBA_REQUIRE(H >= 1 && n_tokens >= 0, MOBA_ERR_ARG, "bad sizes");
   if (int rc = check16(dtype)) return rc;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const int64_t n = n_tokens * H;
   if (n == 0) return 0;
   const unsigned grid = static_cast<unsigned>((n + 7) / 8);
@@ -225,7 +225,7 @@ extern "C" int moba_merge_dq(void* dq, int32_t dtype, int32_t H, const moba_plan
   MOBA_REQUIRE(info->kk >= 0 && info->kk <= 32, MOBA_ERR_ARG, "kk=%d outside [0, 32]", info->kk);
   if (info->kk > 0) MOBA_REQUIRE(part_dq && row_of, MOBA_ERR_ARG, "null partial buffers");
   if (int rc = check16(dtype)) return rc;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const int64_t n = static_cast<int64_t>(info->total_tokens) * H;
   if (n == 0) return 0;
   const unsigned grid = static_cast<unsigned>((n + 7) / 8);
@@ -248,7 +248,7 @@ extern "C" int moba_gather_rows(const void* q, const void* d_out, const float* l
                MOBA_ERR_ARG, "null pointer argument");
   MOBA_REQUIRE(H >= 1, MOBA_ERR_ARG, "H=%d must be >= 1", H);
   if (int rc = check16(dtype)) return rc;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const int64_t nw = info->max_work_tiles_per_head * H;
   if (info->kk == 0 || nw == 0) return 0;
   MOBA_REQUIRE(nw < (1ll << 31), MOBA_ERR_LIMIT, "too many gathered tiles");

@@ -215,7 +215,7 @@ int moba_plan_fill(const int32_t* cu_seqlens_host, int32_t batch, int32_t chunk_
 
 int moba_check_status(const int32_t* status_dev, int32_t device, void* stream) {
   MOBA_REQUIRE(status_dev, MOBA_ERR_ARG, "null pointer argument");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   int32_t h = 0;
   MOBA_CUDA_OK(cudaMemcpyAsync(&h, status_dev, sizeof(h), cudaMemcpyDeviceToHost,
                                static_cast<cudaStream_t>(stream)));

@@ -128,7 +128,7 @@ extern "C" int moba_pool_keys(const void* k, int32_t dtype, int32_t H, int64_t s
   if (rc) return rc;
   MOBA_REQUIRE(pool_ws && kmean, MOBA_ERR_ARG, "null pointer argument");
   MOBA_REQUIRE(info->n_qtiles <= 2147483647 && (H * 16 + 127) / 128 <= 65535, MOBA_ERR_LIMIT, "grid too large");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const PlanDev plan = make_plan_dev(info, meta_dev);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
@@ -167,7 +167,7 @@ int pool_scratch_address(int device, float** out) {
   MOBA_REQUIRE(device >= 0 && device < kMaxDevices, MOBA_ERR_ARG, "device ordinal %d out of range", device);
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_ptr[device]) {
-    MOBA_CUDA_OK(cudaSetDevice(device));
+    MOBA_SET_DEVICE(device);
     void* p = nullptr;
     MOBA_CUDA_OK(cudaGetSymbolAddress(&p, g_pool_scratch));
     g_scratch_ptr[device] = static_cast<float*>(p);
@@ -197,7 +197,7 @@ extern "C" int moba_pool_keys_static(const void* k, int32_t dtype, int32_t H, in
   float* ws = nullptr;
   rc = pool_scratch_address(device, &ws);     // first call on a device: symbol lookup (do it before any capture)
   if (rc) return rc;
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   const PlanDev plan = make_plan_dev(info, meta_dev);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {

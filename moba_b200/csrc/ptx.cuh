@@ -52,13 +52,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Shared abort word + global status word. One instance lives in each CTA's shared memory.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;     // ~2 s of wall time
 struct WaitCtx {
   volatile int* abort_smem;   // set to 1 by the first waiter that gives up
   int* status_gmem;           // device status word the host reads after the launch
+  unsigned long long limit_ns = kWaitLimitNs;   // how long one wait may last
 };
 
-// Wait for `parity` on `bar`, but for no longer than ~2 s of wall time. Returns false when the
-// wait was abandoned (by this thread or, earlier, by any other thread of the CTA).
+// Wait for `parity` on `bar`, but for no longer than ctx.limit_ns (~2 s unless the kernel says otherwise).
+// Returns false when the wait was abandoned (by this thread or, earlier, by any other thread of the CTA).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -67,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 255u) == 0u) {
       if (*ctx.abort_smem) return false;
-      if (globaltimer_ns() - t0 > 2000000000ull) {
+      if (globaltimer_ns() - t0 > ctx.limit_ns) {
         *ctx.abort_smem = 1;
         atomicCAS(ctx.status_gmem, kStatusOk, kStatusWaitTimeout);
         return false;
@@ -113,7 +115,7 @@ __device__ __forceinline__ bool mbar_wait_all(const BarPhase (&w)[N], const Wait
     if (it == 0) t0 = globaltimer_ns();
     if ((++it & 255u) == 0u) {
       if (*ctx.abort_smem) return false;
-      if (globaltimer_ns() - t0 > 2000000000ull) {
+      if (globaltimer_ns() - t0 > ctx.limit_ns) {
         *ctx.abort_smem = 1;
         atomicCAS(ctx.status_gmem, kStatusOk, kStatusWaitTimeout);
         return false;

@@ -166,7 +166,7 @@ extern "C" int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_
   MOBA_REQUIRE(mode >= 0 && mode <= 4, MOBA_ERR_ARG, "mode=%d out of range", mode);
   MOBA_REQUIRE(a_rows >= 128 && (mode != 3 || row_idx), MOBA_ERR_ARG, "mode 3 needs row_idx and a_rows >= 128");
   MOBA_REQUIRE(dtype == MOBA_DTYPE_BF16 || dtype == MOBA_DTYPE_F16, MOBA_ERR_ARG, "dtype must be bf16 or f16");
-  MOBA_CUDA_OK(cudaSetDevice(device));
+  MOBA_SET_DEVICE(device);
   CUtensorMap ma, mb;
   int rc = make_tensor_map_shd(&ma, a, dtype, 128, 1, 128, 128, 128);
   if (rc) return rc;
@@ -186,217 +186,50 @@ extern "C" int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Tensor-pipe rate probe (diagnostic, not on any product path): every CTA issues `iters` groups of eight
-// UMMA instructions of one shape on resident (zero) operands and reports the elapsed SM clocks.
-//   mode 0: SS 128x128x16   mode 1: SS 128x64x16   mode 2: TS 128x128x16 (B MN-major)   mode 3: SS 128x256x16
-//   mode 4: TS 128x64x16... (A from TMEM, B K-major, N = 64)
+// Failure-path self test: a CTA allocates tensor memory and waits on an mbarrier that nothing arrives on, with
+// the wait limit given by the caller. The wait must run out, set the status word to 1 (kStatusWaitTimeout),
+// and the CTA must still release its tensor memory and return, leaving the context usable.
 namespace moba {
 namespace {
 
-struct __align__(1024) RateSmem {
-  uint8_t a[2][16384];
-  uint8_t b[4][16384];
-  uint64_t bar;
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-template <int kMode>
-__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, long long* cycles, int* status) {
-  extern __shared__ uint8_t smem_raw[];
-  RateSmem& sm = *reinterpret_cast<RateSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int tid = threadIdx.x, warp = tid >> 5;
-  WaitCtx wctx{&sm.abort_flag, status};
-  for (int i = tid; i < (int)(sizeof(sm.a) + sizeof(sm.b)) / 16; i += 128)
-    reinterpret_cast<uint4*>(sm.a)[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) {
-    sm.abort_flag = 0;
-    mbar_init(&sm.bar, 1);
+__global__ void __launch_bounds__(128, 1) wait_timeout_kernel(unsigned long long limit_ns, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(&sm.tmem_base, 512);
+    tmem_alloc(&tmem_base, 32);
     tmem_relinquish();
   }
-  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem = sm.tmem_base;
-  if (tid == 0 && kMode < 9) {
-    // descriptors are built once; the loop only adds constant offsets (in 16-byte units) to them
-    const uint64_t a_k = umma_smem_desc(smem_u32(sm.a[0]), 16, 1024);
-    const uint64_t b_k = umma_smem_desc(smem_u32(sm.b[0]), 16, 1024);
-    const uint64_t b_mn = umma_smem_desc(smem_u32(sm.b[0]), 16384, 1024);
-    const long long t0 = clock64();
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = ((ks >> 2) * 16384u + (ks & 3) * 32u) >> 4;
-        if constexpr (kMode == 0)
-          umma_ss(tmem, a_k + off, b_k + off, umma_idesc(128, 128, true, false, false), 1);
-        else if constexpr (kMode == 1)
-          umma_ss(tmem, a_k + off, b_k + off, umma_idesc(128, 64, true, false, false), 1);
-        else if constexpr (kMode == 2)
-          umma_ts(tmem, tmem + 256 + ks * 8, b_mn + ((ks * 2048u) >> 4), umma_idesc(128, 128, true, false, true), 1);
-        else if constexpr (kMode == 3)
-          umma_ss(tmem, a_k + off, b_k + (((ks >> 2) * 32768u + (ks & 3) * 32u) >> 4), umma_idesc(128, 256, true, false, false), 1);
-        else if constexpr (kMode == 4)
-          umma_ts(tmem, tmem + 256 + ks * 8, b_k + off, umma_idesc(128, 64, true, false, false), 1);
-        else if constexpr (kMode == 5)   // SS 128x128, two accumulators alternating
-          umma_ss(tmem + (ks & 1) * 128, a_k + off, b_k + off, umma_idesc(128, 128, true, false, false), 1);
-        else if constexpr (kMode == 6)   // SS 128x64, four accumulators alternating
-          umma_ss(tmem + (ks & 3) * 64, a_k + off, b_k + off, umma_idesc(128, 64, true, false, false), 1);
-        else if constexpr (kMode == 7)   // TS 128x128, two accumulators alternating
-          umma_ts(tmem + (ks & 1) * 128, tmem + 256 + ks * 8, b_mn + ((ks * 2048u) >> 4), umma_idesc(128, 128, true, false, true), 1);
-        else                             // SS 128x128 without accumulation (D overwritten)
-          umma_ss(tmem + (ks & 1) * 128, a_k + off, b_k + off, umma_idesc(128, 128, true, false, false), 0);
-      }
-    }
-    umma_commit(&sm.bar);
-    mbar_wait(&sm.bar, 0, wctx);
-    cycles[blockIdx.x] = clock64() - t0;
-  }
-  if (warp == 3 && kMode == 15) {
-    // Cost of a wait on a barrier whose phase is already complete, nothing else running: eight waits by all 32
-    // lanes, eight by lane 0 with a shuffle broadcast, eight single try_wait instructions by all lanes.
-    __shared__ uint64_t bar_c;
-    if ((tid & 31) == 0) {
-      mbar_init(&bar_c, 1);
-      mbar_fence_init();
-      mbar_arrive(&bar_c);
-    }
-    __syncwarp();
-    long long t[4];
-    bool ok = true;
-    t[0] = clock64();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ok = ok && __all_sync(0xffffffffu, mbar_wait(&bar_c, 0, wctx));
-    t[1] = clock64();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int o = 1;
-      if ((tid & 31) == 0) o = mbar_wait(&bar_c, 0, wctx) ? 1 : 0;
-      ok = ok && __shfl_sync(0xffffffffu, o, 0) != 0;
-    }
-    t[2] = clock64();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ok = ok && mbar_try_wait(&bar_c, 0);
-    t[3] = clock64();
-    if ((tid & 31) == 0) {
-      for (int i = 0; i < 3; ++i) cycles[blockIdx.x * 8 + i] = t[i + 1] - t[i];
-      cycles[blockIdx.x * 8 + 5] = ok ? 1 : 0;
-    }
-  }
-  if (warp == 2 && kMode >= 11 && kMode <= 14) {
-    // Does anything the issuing warp does after tcgen05.commit wait for the committed work? Stamps (SM clocks):
-    // [0] MMAs + commit issued  [1] wait on an already-complete barrier  [2] fence::after_thread_sync
-    // [3] a shared-memory load  [4] wait on the committed barrier (MMAs done). cycles holds 8 slots per CTA.
-    const uint32_t leader = elect_one();
-    __shared__ uint64_t bar_done;
-    if ((tid & 31) == 0) {
-      mbar_init(&bar_done, 1);
-      mbar_fence_init();
-      mbar_arrive(&bar_done);
-    }
-    __syncwarp();
-    const uint64_t a_k = umma_smem_desc(smem_u32(sm.a[0]), 16, 1024);
-    const uint64_t b_k = umma_smem_desc(smem_u32(sm.b[0]), 16, 1024);
-    long long t[6];
-    t[0] = clock64();
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = ((ks >> 2) * 16384u + (ks & 3) * 32u) >> 4;
-        if constexpr (kMode == 14)   // A from TMEM: half the shared-memory operand traffic
-          umma_ts_w(leader, tmem + (ks & 1) * 128, tmem + 256 + ks * 8, b_k + off, umma_idesc(128, 128, true, false, false), 1);
-        else
-          umma_ss_w(leader, tmem + (ks & 1) * 128, a_k + off, b_k + off, umma_idesc(128, 128, true, false, false), 1);
-      }
-    }
-    // mode 11: commit, then wait with try_wait; 12: wait first, commit afterwards; 13: commit, wait with test_wait
-    if constexpr (kMode != 12) umma_commit_w(leader, &sm.bar);
-    t[1] = clock64();
-    bool ok1 = true;
-    if constexpr (kMode == 13) {
-      uint32_t done = 0;
-      for (int spin = 0; spin < 100000 && !done; ++spin)
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(smem_u32(&bar_done)), "r"(0) : "memory");
-      ok1 = done != 0;
-    } else {
-      ok1 = __all_sync(0xffffffffu, mbar_wait(&bar_done, 0, wctx));
-    }
-    t[2] = clock64();
-    if constexpr (kMode == 12) umma_commit_w(leader, &sm.bar);
-    tc_fence_after_sync();
-    t[3] = clock64();
-    const int x = *reinterpret_cast<volatile int*>(&sm.abort_flag);
-    t[4] = clock64() + (x & 0);
-    const bool ok2 = __all_sync(0xffffffffu, mbar_wait(&sm.bar, 0, wctx));
-    t[5] = clock64();
-    if ((tid & 31) == 0) {
-      for (int i = 0; i < 5; ++i) cycles[blockIdx.x * 8 + i] = t[i + 1] - t[i];
-      cycles[blockIdx.x * 8 + 5] = (ok1 && ok2) ? 1 : 0;
-    }
-  }
-  if (warp == 1 && (kMode == 9 || kMode == 10)) {
-    // warp-converged issue: all lanes run the loop, one elected lane issues
-    const uint32_t leader = elect_one();
-    const uint64_t a_k = umma_smem_desc(smem_u32(sm.a[0]), 16, 1024);
-    const uint64_t b_k = umma_smem_desc(smem_u32(sm.b[0]), 16, 1024);
-    const long long t0 = clock64();
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = ((ks >> 2) * 16384u + (ks & 3) * 32u) >> 4;
-        if constexpr (kMode == 9)
-          umma_ss_w(leader, tmem + (ks & 3) * 64, a_k + off, b_k + off, umma_idesc(128, 64, true, false, false), 1);
-        else
-          umma_ss_w(leader, tmem + (ks & 1) * 128, a_k + off, b_k + off, umma_idesc(128, 32, true, false, false), 1);
-      }
-    }
-    umma_commit_w(leader, &sm.bar);
-    mbar_wait(&sm.bar, 0, wctx);
-    if ((tid & 31) == 0) cycles[blockIdx.x] = clock64() - t0;
-  }
+  WaitCtx wctx{&abort_flag, status, limit_ns};
+  // every thread waits; the first whose limit runs out raises the CTA's abort flag, the others follow it
+  mbar_wait(&bar, 0, wctx);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (warp == 0) tmem_dealloc(tmem_base, 32);
 }
 
 }  // namespace
 }  // namespace moba
 
-extern "C" int moba_selftest_mma_rate(int32_t mode, int32_t iters, int32_t n_ctas, long long* cycles,
-                                      int32_t* status, int32_t device, void* stream) {
+extern "C" int moba_selftest_wait_timeout(int64_t limit_ns, int32_t n_ctas, int32_t* status, int32_t device,
+                                          void* stream) {
   using namespace moba;
-  MOBA_REQUIRE(cycles && status && iters > 0 && n_ctas > 0 && mode >= 0 && mode <= 15, MOBA_ERR_ARG, "bad argument");
-  MOBA_CUDA_OK(cudaSetDevice(device));
-  const size_t smem = sizeof(RateSmem) + 1024;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  auto run = [&](auto kern) -> int {
-    MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<n_ctas, 128, smem, st>>>(iters, cycles, status);
-    MOBA_CUDA_OK(cudaGetLastError());
-    return 0;
-  };
-  switch (mode) {
-    case 0: return run(mma_rate_kernel<0>);
-    case 1: return run(mma_rate_kernel<1>);
-    case 2: return run(mma_rate_kernel<2>);
-    case 3: return run(mma_rate_kernel<3>);
-    case 4: return run(mma_rate_kernel<4>);
-    case 5: return run(mma_rate_kernel<5>);
-    case 6: return run(mma_rate_kernel<6>);
-    case 7: return run(mma_rate_kernel<7>);
-    case 8: return run(mma_rate_kernel<8>);
-    case 9: return run(mma_rate_kernel<9>);
-    case 10: return run(mma_rate_kernel<10>);
-    case 11: return run(mma_rate_kernel<11>);
-    case 12: return run(mma_rate_kernel<12>);
-    case 13: return run(mma_rate_kernel<13>);
-    case 14: return run(mma_rate_kernel<14>);
-    default: return run(mma_rate_kernel<15>);
-  }
+  MOBA_REQUIRE(status, MOBA_ERR_ARG, "null pointer argument");
+  MOBA_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000ll, MOBA_ERR_ARG, "limit_ns=%lld outside [1e3, 1e8]",
+               (long long)limit_ns);
+  MOBA_REQUIRE(n_ctas >= 1 && n_ctas <= 1024, MOBA_ERR_ARG, "n_ctas=%d outside [1, 1024]", n_ctas);
+  MOBA_SET_DEVICE(device);
+  wait_timeout_kernel<<<n_ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned long long>(limit_ns), status);
+  MOBA_CUDA_OK(cudaGetLastError());
+  return 0;
 }

@@ -103,7 +103,7 @@ def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk):
         kg = k if k.stride(2) == 1 else k.contiguous()
         kmean = ops.pool_keys(kg, plan)
         sel, _, tile_cnt = ops.gate_topk(qg, kmean, plan, status=status)
-        list_off, work_off, list_tok, row_of = ops.build_lists(plan, H, sel, tile_cnt)
+        list_off, work_off, list_tok, row_of = ops.build_lists(plan, H, sel, tile_cnt, status=status)
         lists = (list_off, work_off, list_tok)
     else:
         # moba_topk == 1 or every sequence is a single chunk: plain causal attention over whole sequences

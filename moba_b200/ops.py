@@ -82,8 +82,8 @@ class Plan:
         meta = torch.empty(max(self.info.meta_ints, 1), dtype=torch.int32, pin_memory=self.device.type == "cuda")
         call("moba_plan_fill", arr, batch, self.chunk_size, self.topk, ctypes.byref(self.info),
              ctypes.c_void_p(meta.data_ptr()))
-        self.meta_host = meta
-        self.meta = meta.to(self.device, non_blocking=False) if self.device.type == "cuda" else meta
+        self.meta_host = meta          # pinned and kept alive by the plan: the upload below is asynchronous
+        self.meta = meta.to(self.device, non_blocking=True) if self.device.type == "cuda" else meta
 
     def table(self, name):
         """Host view of one integer table (for tests)."""
@@ -131,14 +131,40 @@ class PlanView:
         return self.info.rows_per_head * H
 
 
-_PLAN_CACHE = OrderedDict()
+_PLAN_CACHE = OrderedDict()        # (tensor identity, version, chunk, topk, device) -> (tensor, plan)
+_PLAN_BY_VALUE = OrderedDict()     # (cu_seqlens values, chunk, topk, device) -> plan
 _PLAN_CACHE_MAX = 16
+_CU_HOST = {}                      # id(tensor) -> (weak reference, host values) registered by the tensor's maker
+
+
+def register_cu_seqlens(tensor, values):
+    """Tells get_plan the host values of a cu_seqlens tensor whose maker knows them (the layer wrapper builds
+    cu_seqlens from batch and kv_len), so that no device-to-host copy is needed to plan for it."""
+    import weakref
+
+    key = id(tensor)
+    _CU_HOST[key] = (weakref.ref(tensor, lambda _: _CU_HOST.pop(key, None)), tuple(int(x) for x in values))
+
+
+def _plan_for_values(values, chunk_size, topk, device):
+    key = (tuple(values), int(chunk_size), int(topk), str(device))
+    plan = _PLAN_BY_VALUE.get(key)
+    if plan is None:
+        plan = Plan(values, chunk_size, topk, device)
+        _PLAN_BY_VALUE[key] = plan
+        while len(_PLAN_BY_VALUE) > _PLAN_CACHE_MAX:
+            _PLAN_BY_VALUE.popitem(last=False)
+    else:
+        _PLAN_BY_VALUE.move_to_end(key)
+    return plan
 
 
 def get_plan(cu_seqlens, chunk_size, topk, device):
-    """Plan for a cu_seqlens tensor (device or host) or a list. Tensor plans are cached by tensor identity and
-    version, as the reference caches calc_chunks by tensor identity (moba/moba_efficient.py:14); the first
-    call for a device tensor copies it to the host once."""
+    """Plan for a cu_seqlens tensor (device or host) or a list. Plans are cached twice: by tensor identity and
+    version, as the reference caches calc_chunks by tensor identity (moba/moba_efficient.py:14), and by the
+    values themselves, so that equal batches share one plan (and one upload of its tables) whatever tensor
+    carries them. A device tensor whose values were not registered (register_cu_seqlens) is copied to the host
+    once per identity."""
     if isinstance(cu_seqlens, torch.Tensor):
         key = (id(cu_seqlens), cu_seqlens._version, int(chunk_size), int(topk), str(device))
         hit = _PLAN_CACHE.get(key)
@@ -147,12 +173,17 @@ def get_plan(cu_seqlens, chunk_size, topk, device):
             return hit[1]
         if cu_seqlens.dtype not in (torch.int32, torch.int64) or cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2:
             raise ValueError("cu_seqlens must be a 1-D int32 tensor with at least two entries")
-        plan = Plan(cu_seqlens.detach().cpu().tolist(), chunk_size, topk, device)
+        known = _CU_HOST.get(id(cu_seqlens))
+        if known is not None and known[0]() is cu_seqlens and cu_seqlens._version == 0:
+            values = known[1]
+        else:
+            values = cu_seqlens.detach().cpu().tolist()
+        plan = _plan_for_values(values, chunk_size, topk, device)
         _PLAN_CACHE[key] = (cu_seqlens, plan)
         while len(_PLAN_CACHE) > _PLAN_CACHE_MAX:
             _PLAN_CACHE.popitem(last=False)
         return plan
-    return Plan(list(cu_seqlens), chunk_size, topk, device)
+    return _plan_for_values([int(x) for x in cu_seqlens], chunk_size, topk, device)
 
 
 def new_status(device):
@@ -215,8 +246,9 @@ def gate_topk(q, kmean, plan, want_scores=False, status=None, fma=False):
     return sel, scores, tile_cnt
 
 
-def build_lists(plan, H, sel, tile_cnt):
-    """Returns (list_off [E+1], work_off [E+1], list_tok [R*H], row_of [S,H,kk]); E = n_chunks*H."""
+def build_lists(plan, H, sel, tile_cnt, status=None):
+    """Returns (list_off [E+1], work_off [E+1], list_tok [R*H], row_of [S,H,kk]); E = n_chunks*H. A chunk id in
+    `sel` that is not a candidate of its query is skipped and reported through `status` (2 = bad index)."""
     dev = sel.device
     E = plan.info.n_chunks * H
     list_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
@@ -225,7 +257,8 @@ def build_lists(plan, H, sel, tile_cnt):
     row_of = torch.empty_like(sel)
     with _timed("build_lists", dev):
         call("moba_build_lists", H, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(sel), _ptr(tile_cnt),
-             _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(row_of), _dev_index(sel), _stream(dev))
+             _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(row_of), _ptr(status), _dev_index(sel),
+             _stream(dev))
     return list_off, work_off, list_tok, row_of
 
 
@@ -393,3 +426,10 @@ def selftest_umma(mode, a, b):
          _stream(a.device))
     check_status(status)
     return c
+
+
+def selftest_wait_timeout(status, limit_ns=1_000_000, n_ctas=4):
+    """Launches CTAs that wait on a barrier nothing arrives on; the waits run out after limit_ns and set `status`
+    (a zeroed device word) to 1. The kernel frees its tensor memory and returns."""
+    call("moba_selftest_wait_timeout", int(limit_ns), int(n_ctas), _ptr(status), _dev_index(status),
+         _stream(status.device))

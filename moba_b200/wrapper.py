@@ -16,6 +16,29 @@ def fa_to_hf(x: torch.Tensor, batch: int):
     return x.view(batch, -1, x.shape[1], x.shape[2]).permute(0, 2, 1, 3)
 
 
+_CU_CACHE = {}
+
+
+def _cu_seqlens(batch, kv_len, device):
+    """cumsum([0] + [kv_len] * batch) as an int32 tensor on `device` (moba/wrapper.py:62-66), made once per
+    (batch, kv_len, device): every layer of a model then hands the same tensor to the attention call, whose plan
+    cache works by tensor identity, and the host values are registered with it so that planning never reads the
+    device tensor back."""
+    key = (int(batch), int(kv_len), str(device))
+    t = _CU_CACHE.get(key)
+    if t is None:
+        values = [i * int(kv_len) for i in range(int(batch) + 1)]
+        t = torch.tensor(values, dtype=torch.int32, device=device)
+        if t.is_cuda:
+            from . import ops
+
+            ops.register_cu_seqlens(t, values)
+        if len(_CU_CACHE) >= 64:
+            _CU_CACHE.clear()
+        _CU_CACHE[key] = t
+    return t
+
+
 def _decode_attention(query, key, value, scaling):
     """Dense causal attention for the decode phase (q_len != kv_len), bottom-right aligned as the reference's
     flash_attn_func(..., causal=True) call (moba/wrapper.py:76-82); returns [batch, q_len, heads, dim].
@@ -33,13 +56,14 @@ def _decode_attention(query, key, value, scaling):
         from .moba_efficient import _status_word
 
         return ops.decode_attn(query, key, value, scaling, status=_status_word(query.device))
-    if hkv != hq:
-        key = key.repeat_interleave(hq // hkv, dim=1)
-        value = value.repeat_interleave(hq // hkv, dim=1)
+    if lk < lq:
+        raise ValueError(f"decode needs kv_len >= q_len (got q_len {lq}, kv_len {lk}): the causal mask is aligned to "
+                         "the end of the keys, so earlier query positions would see no key at all")
     qi = torch.arange(lq, device=query.device)[:, None] + (lk - lq)
     ki = torch.arange(lk, device=query.device)[None, :]
     mask = ki <= qi
-    out = torch.nn.functional.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling)
+    out = torch.nn.functional.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling,
+                                                           enable_gqa=hkv != hq)
     return out.transpose(1, 2)
 
 
@@ -82,11 +106,7 @@ def moba_layer(
             kv_replicas = q_heads // kv_heads
             key = torch.repeat_interleave(key, kv_replicas, dim=1)
             value = torch.repeat_interleave(value, kv_replicas, dim=1)
-        cu_seqlens_k = torch.cumsum(
-            torch.tensor([0] + [kv_len] * batch, device=query.device),
-            dim=0,
-            dtype=torch.int32,
-        )
+        cu_seqlens_k = _cu_seqlens(batch, kv_len, query.device)
         out = moba_impl(
             q=query,
             k=key,

@@ -149,3 +149,64 @@ def test_decode_branch_matches_dense_causal():
     s = s.masked_fill(~mask, float("-inf"))
     ref = torch.einsum("bhqk,bhkd->bhqd", s.softmax(-1), vv).transpose(1, 2)
     torch.testing.assert_close(out, ref, atol=1e-5, rtol=1e-5)
+
+
+def test_register_moba_registers_both_reference_keys(monkeypatch):
+    """moba/__init__.py:9-11 registers "moba" and "moba_naive"; the second forwards to the reference package's dense
+    oracle and says so clearly when that package is not importable."""
+    import builtins
+
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+    import moba_b200
+
+    moba_b200.register_moba(moba_b200.MoBAConfig(512, 3))
+    assert "moba" in ALL_ATTENTION_FUNCTIONS and "moba_naive" in ALL_ATTENTION_FUNCTIONS
+    real_import = builtins.__import__
+
+    def no_reference(name, *a, **k):
+        if name.startswith("moba.") or name == "moba":
+            raise ImportError("no reference package")
+        return real_import(name, *a, **k)
+
+    monkeypatch.setattr(builtins, "__import__", no_reference)
+    with pytest.raises(RuntimeError, match='attn_implementation="moba"'):
+        moba_b200._moba_naive_impl()
+
+
+def test_plans_are_shared_by_value_and_wrapper_cu_seqlens_by_identity():
+    from moba_b200 import ops
+    from moba_b200.wrapper import _cu_seqlens
+
+    a = ops.get_plan([0, 100, 356], 64, 3, "cpu")
+    b = ops.get_plan(torch.tensor([0, 100, 356], dtype=torch.int32), 64, 3, "cpu")
+    assert a is b                                              # equal values: one plan, one table upload
+    assert ops.get_plan([0, 100, 356], 64, 4, "cpu") is not a
+    t1 = _cu_seqlens(3, 40, torch.device("cpu"))
+    assert t1.tolist() == [0, 40, 80, 120] and t1.dtype == torch.int32
+    assert _cu_seqlens(3, 40, torch.device("cpu")) is t1       # every layer call sees the same tensor
+
+    class NoReadBack(torch.Tensor):
+        pass
+
+    t = torch.tensor([0, 128, 256], dtype=torch.int32)
+    ops.register_cu_seqlens(t, [0, 128, 256])
+    calls = []
+    orig = torch.Tensor.cpu
+    try:
+        torch.Tensor.cpu = lambda self, *a, **k: calls.append(1) or orig(self, *a, **k)
+        p = ops.get_plan(t, 128, 2, "cpu")
+    finally:
+        torch.Tensor.cpu = orig
+    assert not calls and p.info.total_tokens == 256            # registered host values: no read-back of the tensor
+
+
+def test_decode_branch_rejects_more_queries_than_keys():
+    from moba_b200 import MoBAConfig, moba_layer
+
+    class M(torch.nn.Module):
+        is_causal = True
+
+    q, k = torch.randn(1, 2, 5, 16), torch.randn(1, 2, 3, 16)
+    with pytest.raises(ValueError, match="kv_len >= q_len"):
+        moba_layer(None, MoBAConfig(4, 2), M(), q, k, k)
