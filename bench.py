@@ -98,6 +98,20 @@ def read_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+def read_traffic_table():
+    """(chunk, top-k, lengths, kernel) -> DRAM bytes per head and launch, from profiles/dram_traffic_per_head.txt
+    (lines: kernel chunk topk tokens bytes_per_head; '#' starts a comment). Empty when the file is missing."""
+    table = {}
+    path = os.path.join(ROOT, "profiles", "dram_traffic_per_head.txt")
+    if os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                fields = line.split("#")[0].split()
+                if len(fields) == 5:
+                    table[(int(fields[1]), int(fields[2]), (int(fields[3]),), fields[0])] = float(fields[4])
+    return table
+
+
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -464,21 +478,21 @@ def run_ours(args, cfg_id, cfg):
         flops = (14 if cfg["backward"] else 4) * D * pairs
         value = flops / (ms_step * 1e-3) / 1e12
         pairs_local = pairs // world
-        # executed tile products per kernel group: the forward runs 2 products per (query tile, key tile) pair, the
-        # key/value-side backward 4 (S^T, dP^T, dV, dK) and the query-side backward 3 (S, dP, dQ): the split
-        # backward recomputes S and dP, so it executes 14 D pairs where 10 D pairs are counted
-        group_flops = {"attn_fwd": 4 * D * pairs_local, "attn_bwd_dkdv": 8 * D * pairs_local,
-                       "attn_bwd_dq": 6 * D * pairs_local}
+        # tile products per kernel group: the forward runs 2 products per (query tile, key tile) pair and the
+        # one-pass backward 5 -- the counted 4 * D and 10 * D per pair, nothing recomputed. (The two-kernel backward
+        # kept for comparison runs executes 4 + 3 products: its entries are executed work, not counted work.)
+        group_flops = {"attn_fwd": 4 * D * pairs_local, "attn_bwd": 10 * D * pairs_local,
+                       "attn_bwd_dkdv": 8 * D * pairs_local, "attn_bwd_dq": 6 * D * pairs_local}
         dom = max((n for n in group_flops if n in kernel_ms), key=lambda n: kernel_ms[n], default=None)
         roofline = None
         if dom:
             ach = group_flops[dom] / (kernel_ms[dom] * 1e-3) / 1e12
             peak = peaks["bf16_tflops_sustained"]
-            # DRAM bytes per launch from the committed ncu capture of a 4-head slice of this workload
-            # (profiles/attention_tiles_config31_ncu_full.md); traffic is proportional to the heads a launch covers
+            # DRAM bytes per launch: measured per head on a 4-head slice of this workload (one ncu capture per
+            # kernel, listed in the traffic table next to the profiles); proportional to the heads a launch covers
             traffic = None
-            if cfg["lens"] == [131072] and cfg["chunk"] == 4096 and cfg["topk"] == 12 and cfg["backward"]:
-                per_head = {"attn_fwd": 2.49e9 / 4, "attn_bwd_dkdv": 3.66e9 / 4, "attn_bwd_dq": 5.08e9 / 4}[dom]
+            per_head = read_traffic_table().get((cfg["chunk"], cfg["topk"], tuple(cfg["lens"]), dom))
+            if per_head is not None:
                 traffic = per_head * (H // world)
             roofline = {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                         "frac": ach / peak, "traffic": traffic, "peak_source": peaks["source"] + " (sustained bf16)",
@@ -611,12 +625,14 @@ def run_decode(args, cfg_id, cfg):
 
 def launches_per_step(cfg, world):
     """Kernels of libmoba_b200.so launched per step: pool 2, gate 1, lists 3, forward tiles 2, merge 1, and in
-    backward delta 1, row gather 1, dK/dV 1, dQ 2, dq merge 1. A forward-only run on several GPUs works in two
-    head groups (twice the forward launches)."""
+    backward delta 1, row gather 1, the one-pass tile backward 1, dq merge 1. A forward-only run on several GPUs
+    works in two head groups (twice the forward launches)."""
     hl = cfg["heads"] // world
     if world > 1 and not cfg["backward"] and hl >= 2:
         return 18
-    return 9 + (6 if cfg["backward"] else 0)
+    from moba_b200 import moba_efficient
+
+    return 9 + ((6 if moba_efficient.SPLIT_BACKWARD else 4) if cfg["backward"] else 0)
 
 
 def main():

@@ -46,6 +46,7 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
   const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
 
   if (tid == 0) {
+    // TMA brings A in modes 0, 3, 4, 5 and B in every mode but 5 (threads write it there)
     const uint32_t bytes = ((mode == 0 || mode == 3 || mode == 4) ? 4u : 2u) * 16384u;
     mbar_arrive_expect_tx(&sm.bar_load, bytes);
     if (mode == 3) {
@@ -56,12 +57,14 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
         tma_gather4_2d(smem_u32(sm.a[1]) + r * 128, &map_rows, &sm.bar_load, 64, i0, i1, i2, i3);
       }
     }
-    if (mode == 0 || mode == 4) {
+    if (mode == 0 || mode == 4 || mode == 5) {
       tma_load_3d(smem_u32(sm.a[0]), &map_a, &sm.bar_load, 0, 0, 0);
       tma_load_3d(smem_u32(sm.a[1]), &map_a, &sm.bar_load, 64, 0, 0);
     }
-    tma_load_3d(smem_u32(sm.b[0]), &map_b, &sm.bar_load, 0, 0, 0);
-    tma_load_3d(smem_u32(sm.b[1]), &map_b, &sm.bar_load, 64, 0, 0);
+    if (mode != 5) {
+      tma_load_3d(smem_u32(sm.b[0]), &map_b, &sm.bar_load, 0, 0, 0);
+      tma_load_3d(smem_u32(sm.b[1]), &map_b, &sm.bar_load, 64, 0, 0);
+    }
   }
 
   if (mode == 1) {
@@ -84,6 +87,12 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
       *reinterpret_cast<uint4*>(sm.x[0] + nosw_offset(tid, ch)) = ra[ch];
       *reinterpret_cast<uint4*>(sm.x[1] + nosw_offset(tid, ch)) = rb[ch];
     }
+    fence_proxy_async_smem();
+  } else if (mode == 5) {
+    // thread = row k of B: its first 64 elements as eight 16-byte chunks of one swizzled 128-byte row
+    const uint4* rb = reinterpret_cast<const uint4*>(b_gmem + static_cast<size_t>(tid) * 128);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(sm.b[0] + sw128_offset(tid, ch)) = rb[ch];
     fence_proxy_async_smem();
   } else if (mode == 2) {
     // 16 consecutive threads copy the 16 16-byte chunks of one row; 8 rows per pass
@@ -115,6 +124,13 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
         if (mode == 4)
           umma_ss(tmem, umma_smem_desc_nosw(smem_u32(sm.x[0]), 128, 256), umma_smem_desc_nosw(smem_u32(sm.x[1]), 128, 256),
                   idesc, 1);
+      } else if (mode == 5) {
+        // both operands MN-major, N = 64: C[m, n] = sum_k A[k, m] B[k, n] (the dQ^T = K^T dS^T product of the backward)
+        constexpr uint32_t idesc = umma_idesc(128, 64, kBf16, true, true);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem, umma_smem_desc(smem_u32(sm.a[0]) + ks * 2048u, 16384, 1024),
+                  umma_smem_desc(smem_u32(sm.b[0]) + ks * 2048u, 16384, 1024), idesc, ks > 0);
       } else if (mode == 1) {
         constexpr uint32_t idesc = umma_idesc(128, 128, kBf16, false, true);
 #pragma unroll
@@ -141,8 +157,10 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
       uint32_t r[32];
       tmem_ld32(lane_addr + i * 32, r);
       tmem_wait_ld();
+      // mode 5 produces 64 columns; the rest of its rows is reported as zero
 #pragma unroll
-      for (int j = 0; j < 32; ++j) c[static_cast<size_t>(tid) * 128 + i * 32 + j] = __uint_as_float(r[j]);
+      for (int j = 0; j < 32; ++j)
+        c[static_cast<size_t>(tid) * 128 + i * 32 + j] = (mode == 5 && i >= 2) ? 0.f : __uint_as_float(r[j]);
     }
   }
   tc_fence_before_sync();
@@ -163,7 +181,7 @@ extern "C" int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_
                                          int32_t device, void* stream) {
   using namespace moba;
   MOBA_REQUIRE(a && b && c && status, MOBA_ERR_ARG, "null pointer argument");
-  MOBA_REQUIRE(mode >= 0 && mode <= 4, MOBA_ERR_ARG, "mode=%d out of range", mode);
+  MOBA_REQUIRE(mode >= 0 && mode <= 5, MOBA_ERR_ARG, "mode=%d out of range", mode);
   MOBA_REQUIRE(a_rows >= 128 && (mode != 3 || row_idx), MOBA_ERR_ARG, "mode 3 needs row_idx and a_rows >= 128");
   MOBA_REQUIRE(dtype == MOBA_DTYPE_BF16 || dtype == MOBA_DTYPE_F16, MOBA_ERR_ARG, "dtype must be bf16 or f16");
   MOBA_SET_DEVICE(device);

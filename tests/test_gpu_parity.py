@@ -41,7 +41,7 @@ def check_against_oracle(q, k, v, d_out, cu, chunk, topk, dev, dtype="bf16", tag
 
 # ------------------------------------------------------------------------------------------ building blocks
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
-@pytest.mark.parametrize("mode", [0, 1, 2, 4])
+@pytest.mark.parametrize("mode", [0, 1, 2, 4, 5])
 def test_umma_selftest(cuda_device, mode, dtype):
     from moba_b200 import ops
 
@@ -50,6 +50,9 @@ def test_umma_selftest(cuda_device, mode, dtype):
     b = torch.randn(128, 128, device=cuda_device).to(TORCH_DT[dtype])
     c = ops.selftest_umma(mode, a, b)
     ref = a.float() @ (b.float().T if mode in (0, 4) else b.float())
+    if mode == 5:       # both operands MN-major, 64 result columns
+        ref = torch.zeros_like(ref)
+        ref[:, :64] = a.float().T @ b.float()[:, :64]
     if mode == 4:       # plus a ninth k-step from thread-written tiles without swizzle
         ref = ref + a[:, :16].float() @ b[:, :16].float().T
     assert (c - ref).abs().max().item() < 1e-3
