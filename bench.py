@@ -478,11 +478,11 @@ def run_ours(args, cfg_id, cfg):
         flops = (14 if cfg["backward"] else 4) * D * pairs
         value = flops / (ms_step * 1e-3) / 1e12
         pairs_local = pairs // world
-        # tile products per kernel group: the forward runs 2 products per (query tile, key tile) pair and the
-        # one-pass backward 5 -- the counted 4 * D and 10 * D per pair, nothing recomputed. (The two-kernel backward
-        # kept for comparison runs executes 4 + 3 products: its entries are executed work, not counted work.)
-        group_flops = {"attn_fwd": 4 * D * pairs_local, "attn_bwd": 10 * D * pairs_local,
-                       "attn_bwd_dkdv": 8 * D * pairs_local, "attn_bwd_dq": 6 * D * pairs_local}
+        # executed tile products per kernel group: the forward runs 2 products per (query tile, key tile) pair, the
+        # key/value-side backward 4 (S^T, dP^T, dV, dK) and the query-side backward 3 (S, dP, dQ): the split
+        # backward recomputes S and dP, so it executes 14 D pairs where 10 D pairs are counted
+        group_flops = {"attn_fwd": 4 * D * pairs_local, "attn_bwd_dkdv": 8 * D * pairs_local,
+                       "attn_bwd_dq": 6 * D * pairs_local}
         dom = max((n for n in group_flops if n in kernel_ms), key=lambda n: kernel_ms[n], default=None)
         roofline = None
         if dom:
@@ -625,14 +625,12 @@ def run_decode(args, cfg_id, cfg):
 
 def launches_per_step(cfg, world):
     """Kernels of libmoba_b200.so launched per step: pool 2, gate 1, lists 3, forward tiles 2, merge 1, and in
-    backward delta 1, row gather 1, the one-pass tile backward 1, dq merge 1. A forward-only run on several GPUs
-    works in two head groups (twice the forward launches)."""
+    backward delta 1, row gather 1, dK/dV 1, dQ 2, dq merge 1. A forward-only run on several GPUs works in two
+    head groups (twice the forward launches)."""
     hl = cfg["heads"] // world
     if world > 1 and not cfg["backward"] and hl >= 2:
         return 18
-    from moba_b200 import moba_efficient
-
-    return 9 + ((6 if moba_efficient.SPLIT_BACKWARD else 4) if cfg["backward"] else 0)
+    return 9 + (6 if cfg["backward"] else 0)
 
 
 def main():

@@ -227,26 +227,6 @@ int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_
                      const float* delta_g, const float* lse, const float* delta, float* dq_self,
                      float* part_dq, int32_t parts, int32_t* status, int32_t device, void* stream);
 
-/*
- * Backward of the attention tiles in one pass: dk, dv [S, kv_heads, D] (dtype of q) and the unrounded dq pieces
- * dq_self [S,H,D] / part_dq [R*H, D] (fp32), five tile products per (query tile, key tile) pair and none of them
- * twice. One CTA per (chunk, key/value head, 128-key tile), as in moba_attn_bwd_dkdv; it also forms this key
- * tile's share of dq for every query tile it visits, and the shares of a chunk's key tiles are summed in global
- * memory in a fixed order (key tile 0 first) under per-tile turn counters, so the result is the same bits on every
- * run. Replaces both _flash_attn_varlen_backward calls of moba/moba_efficient.py:208-264 and the autograd scatter
- * through the Q gather and the KV regrouping (:381-386, :406-414).
- *   turn_ws  moba_attn_bwd_ws_ints(info, H) int32 of scratch (the turn counters; cleared by the call)
- *   qg / dog / lse_g / delta_g  list-ordered copies (moba_gather_rows); may be NULL when no list part is requested
- *   parts    as for moba_attn_fwd
- */
-int64_t moba_attn_bwd_ws_ints(const moba_plan_info* info, int32_t H);
-int moba_attn_bwd(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype, int32_t H,
-                  int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv, const moba_plan_info* info,
-                  const int32_t* meta_dev, const int32_t* list_off, const int32_t* work_off, const void* qg,
-                  const void* dog, const float* lse_g, const float* delta_g, const float* lse, const float* delta,
-                  void* dk, void* dv, float* dq_self, float* part_dq, int32_t* turn_ws, int32_t parts,
-                  int32_t* status, int32_t device, void* stream);
-
 /* dq[s,h,:] = round(dq_self[s,h,:] + sum_j part_dq[row_of[s,h,j], :]) (fp32 sum in slot order, one rounding
  * to `dtype`). Replaces the index_select backward (index_add) autograd runs for moba_q
  * (moba/moba_efficient.py:381-386). With info->kk == 0 it only rounds dq_self. */
@@ -296,7 +276,7 @@ int moba_memcpy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pi
  *   mode 4: C = A * B^T + A[:, :16] * B[:, :16]^T   mode 0 plus a ninth k-step from thread-written K-major tiles
  *           without swizzle (the way the dK/dV kernel folds lse / delta into its products)
  *   mode 5: C[:, :64] = A^T * B[:, :64]   both operands MN-major (A [128(K),128(M)] row-major by TMA, B's first 64
- *           columns written by threads with the 128-byte swizzle), N = 64: the dQ^T = K^T dS^T product of the backward
+ *           columns written by threads with the 128-byte swizzle), N = 64
  * a, b: bf16 (dtype 0) or f16 (dtype 1) device buffers of 128*128 elements; c: 128*128 fp32.
  */
 int moba_selftest_umma(int32_t mode, const void* a, const void* b, float* c, int32_t dtype, int32_t* status,

@@ -81,9 +81,6 @@ SIGNATURES = {
                                           _P, _P, _P, _P, _I32, _P, _I32, _P]),
     "moba_attn_bwd_dq": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P,
                                         _P, _P, _P, _P, _P, _P, _I32, _P, _I32, _P]),
-    "moba_attn_bwd_ws_ints": (_I64, [_INFO, _I32]),
-    "moba_attn_bwd": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P,
-                                     _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I32, _P]),
     "moba_memcpy_2d": (ctypes.c_int, [_P, _I64, _P, _I64, _I64, _I64, _I32, _I32, _P]),
     "moba_merge_dq": (ctypes.c_int, [_P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),
     "moba_decode_ws_floats": (_I64, [_I32, _I32, _I32, _I32, _I32]),

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoba_b200.so")
-SOURCES = ["plan.cu", "selftest.cu", "pool.cu", "gate.cu", "gate_umma.cu", "attn_fwd.cu", "merge.cu", "attn_bwd_dkdv.cu", "attn_bwd_dq.cu", "attn_bwd.cu", "hostio.cu", "decode.cu"]
+SOURCES = ["plan.cu", "selftest.cu", "pool.cu", "gate.cu", "gate_umma.cu", "attn_fwd.cu", "merge.cu", "attn_bwd_dkdv.cu", "attn_bwd_dq.cu", "hostio.cu", "decode.cu"]
 
 
 def _sources():

@@ -1,6 +1,6 @@
 // HBM-bound row kernels around the attention tiles: log-sum-exp merge of partial results, the backward row
-// term delta = rowsum(dO * O), and the sum of dq partials. One warp per (token, head) row of 128 elements,
-// each lane owns 4 consecutive elements (8 bytes), partial rows are fetched by index (no atomics, fixed
+// term delta = rowsum(dO * O), and the sum of dq partials. A warp works on one (token, head) row of 128 elements
+// at a time, each lane owns 4 consecutive elements (8 bytes), partial rows are fetched by index (no atomics, fixed
 // summation order).
 #include "common.cuh"
 
@@ -34,89 +34,157 @@ __device__ __forceinline__ uint2 pack4(const float (&f)[4]) {
   return u;
 }
 
+// All three row kernels run a fixed number of warps that stride over the rows. What the next row needs first (its
+// row_of entries, its own row) is requested one iteration ahead and the partial rows of a row are requested
+// together, so a warp keeps several independent loads in flight even when a row has only two or three partials
+// (one warp per row with a row_of -> partial-row chain left too little in flight to fill the memory pipe).
+constexpr int kRowWarps = 8;             // warps per CTA
+
+// As many CTAs as are resident at once (or fewer when there are fewer rows): the warps stride over the rows, so a
+// grid larger than one wave would only add a ragged last wave.
+template <typename Kernel>
+unsigned row_grid(int64_t n_rows, Kernel kern) {
+  int dev = 0, sms = 148, per_sm = 1;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kRowWarps * 32, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const int64_t want = (n_rows + kRowWarps - 1) / kRowWarps;
+  const int64_t cap = static_cast<int64_t>(sms) * per_sm;
+  return static_cast<unsigned>(want < cap ? want : cap);
+}
+
 // Restates MoonshotAI/MoBA moba/moba_efficient.py:118-168: m = max of the partial LSEs, se = sum of
 // exp(lse - m), L = log(se) + m, out = sum_j out_j * exp(lse_j - L). In place on out / lse (the self result).
-template <bool kBf16>
-__global__ void __launch_bounds__(256)
+// KB = partial rows requested together (a row with more slots takes several rounds).
+template <bool kBf16, int KB>
+__global__ void __launch_bounds__(kRowWarps * 32)
 merge_fwd_kernel(uint16_t* __restrict__ out, float* __restrict__ lse, int64_t n_rows, int kk,
                  const uint16_t* __restrict__ part_o, const float* __restrict__ part_lse,
                  const int32_t* __restrict__ row_of) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kRowWarps;
+  int64_t idx = static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
   if (idx >= n_rows) return;
-  const float ls = lse[idx];
-  int r = -1;
-  float lj = -INFINITY;
-  if (lane < kk) {
-    r = row_of[idx * kk + lane];
-    if (r >= 0) lj = part_lse[r];
-  }
-  float m = fmaxf(ls, lj);
+  int r_next = lane < kk ? __ldg(row_of + idx * kk + lane) : -1;
+  for (; idx < n_rows; idx += n_warps) {
+    const int r = r_next;
+    const int64_t nxt = idx + n_warps;
+    if (nxt < n_rows) r_next = lane < kk ? __ldg(row_of + nxt * kk + lane) : -1;
+    const float lj = r >= 0 ? __ldg(part_lse + r) : -INFINITY;
+    // the first KB partial rows need only r: requested together with the partial log-sum-exps
+    uint2 bits[KB];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  const float wj = (r >= 0) ? __expf(lj - m) : 0.f;
-  const float ws = __expf(ls - m);
-  float se = wj;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
-  se += ws;
-  const float inv = 1.0f / se;
-
-  uint2* orow = reinterpret_cast<uint2*>(out + idx * MOBA_HEAD_DIM) + lane;
-  float acc[4], f[4];
-  unpack4<kBf16>(*orow, f);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i] = f[i] * ws;
-  for (int j = 0; j < kk; ++j) {
-    const int rj = __shfl_sync(0xffffffffu, r, j);
-    const float w = __shfl_sync(0xffffffffu, wj, j);
-    if (rj >= 0) {
-      unpack4<kBf16>(__ldg(reinterpret_cast<const uint2*>(part_o + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane), f);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] = fmaf(f[i], w, acc[i]);
+    for (int j = 0; j < KB; ++j) {
+      const int rj = __shfl_sync(0xffffffffu, r, j);
+      bits[j] = (j < kk && rj >= 0)
+                    ? __ldg(reinterpret_cast<const uint2*>(part_o + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane)
+                    : make_uint2(0u, 0u);
     }
-  }
+    uint2* orow = reinterpret_cast<uint2*>(out + idx * MOBA_HEAD_DIM) + lane;
+    const uint2 self_bits = *orow;
+    const float ls = lse[idx];
+    float m = fmaxf(ls, lj);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i] *= inv;
-  *orow = pack4<kBf16>(acc);
-  if (lane == 0) lse[idx] = m + __logf(se);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float wj = (r >= 0) ? __expf(lj - m) : 0.f;
+    const float ws = __expf(ls - m);
+    float se = wj;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    se += ws;
+    const float inv = 1.0f / se;
+    float acc[4], f[4];
+    unpack4<kBf16>(self_bits, f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = f[i] * ws;
+    for (int j0 = 0; j0 < kk; j0 += KB) {
+      if (j0 > 0) {
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+          const int rj = __shfl_sync(0xffffffffu, r, (j0 + j) & 31);
+          bits[j] = (j0 + j < kk && rj >= 0)
+                        ? __ldg(reinterpret_cast<const uint2*>(part_o + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane)
+                        : make_uint2(0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < KB; ++j) {
+        // an empty slot has weight 0 and zero bits
+        const float w = __shfl_sync(0xffffffffu, wj, (j0 + j) & 31);
+        unpack4<kBf16>(bits[j], f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf(f[i], (j0 + j < kk) ? w : 0.f, acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] *= inv;
+    *orow = pack4<kBf16>(acc);
+    if (lane == 0) lse[idx] = m + __logf(se);
+  }
 }
 
 template <bool kBf16>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kRowWarps * 32)
 delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d_out, int64_t n_rows,
              float* __restrict__ delta) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (idx >= n_rows) return;
-  float a[4], b[4];
-  unpack4<kBf16>(__ldg(reinterpret_cast<const uint2*>(out + idx * MOBA_HEAD_DIM) + lane), a);
-  unpack4<kBf16>(__ldg(reinterpret_cast<const uint2*>(d_out + idx * MOBA_HEAD_DIM) + lane), b);
-  float s = a[0] * b[0] + a[1] * b[1] + a[2] * b[2] + a[3] * b[3];
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kRowWarps;
+  // four rows per warp and iteration: eight independent 256-byte loads in flight
+  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5)) * 4; base < n_rows;
+       base += n_warps * 4) {
+    uint2 a[4], b[4];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) delta[idx] = s;
-}
-
-template <bool kBf16>
-__global__ void __launch_bounds__(256)
-merge_dq_kernel(uint16_t* __restrict__ dq, const float* __restrict__ dq_self, int64_t n_rows, int kk,
-                const float* __restrict__ part_dq, const int32_t* __restrict__ row_of) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (idx >= n_rows) return;
-  int r = -1;
-  if (kk > 0 && lane < kk) r = row_of[idx * kk + lane];
-  const float4 s4 = __ldg(reinterpret_cast<const float4*>(dq_self + idx * MOBA_HEAD_DIM) + lane);
-  float acc[4] = {s4.x, s4.y, s4.z, s4.w};
-  for (int j = 0; j < kk; ++j) {
-    const int rj = __shfl_sync(0xffffffffu, r, j);
-    if (rj >= 0) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(part_dq + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane);
-      acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+    for (int i = 0; i < 4; ++i) {
+      const int64_t idx = base + i < n_rows ? base + i : n_rows - 1;
+      a[i] = __ldg(reinterpret_cast<const uint2*>(out + idx * MOBA_HEAD_DIM) + lane);
+      b[i] = __ldg(reinterpret_cast<const uint2*>(d_out + idx * MOBA_HEAD_DIM) + lane);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float x[4], y[4];
+      unpack4<kBf16>(a[i], x);
+      unpack4<kBf16>(b[i], y);
+      float s = x[0] * y[0] + x[1] * y[1] + x[2] * y[2] + x[3] * y[3];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0 && base + i < n_rows) delta[base + i] = s;
     }
   }
-  *(reinterpret_cast<uint2*>(dq + idx * MOBA_HEAD_DIM) + lane) = pack4<kBf16>(acc);
+}
+
+template <bool kBf16, int KB>
+__global__ void __launch_bounds__(kRowWarps * 32)
+merge_dq_kernel(uint16_t* __restrict__ dq, const float* __restrict__ dq_self, int64_t n_rows, int kk,
+                const float* __restrict__ part_dq, const int32_t* __restrict__ row_of) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kRowWarps;
+  int64_t idx = static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
+  if (idx >= n_rows) return;
+  int r_next = (kk > 0 && lane < kk) ? __ldg(row_of + idx * kk + lane) : -1;
+  for (; idx < n_rows; idx += n_warps) {
+    const int r = r_next;
+    const int64_t nxt = idx + n_warps;
+    if (nxt < n_rows) r_next = (kk > 0 && lane < kk) ? __ldg(row_of + nxt * kk + lane) : -1;
+    const float4 s4 = __ldg(reinterpret_cast<const float4*>(dq_self + idx * MOBA_HEAD_DIM) + lane);
+    float acc[4] = {s4.x, s4.y, s4.z, s4.w};
+    for (int j0 = 0; j0 < kk; j0 += KB) {
+      float4 f[KB];
+#pragma unroll
+      for (int j = 0; j < KB; ++j) {
+        const int rj = __shfl_sync(0xffffffffu, r, (j0 + j) & 31);
+        f[j] = (j0 + j < kk && rj >= 0)
+                   ? __ldg(reinterpret_cast<const float4*>(part_dq + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      // summed in slot order (an empty slot adds zero), so the result does not depend on how rows are batched
+#pragma unroll
+      for (int j = 0; j < KB; ++j) {
+        acc[0] += f[j].x; acc[1] += f[j].y; acc[2] += f[j].z; acc[3] += f[j].w;
+      }
+    }
+    *(reinterpret_cast<uint2*>(dq + idx * MOBA_HEAD_DIM) + lane) = pack4<kBf16>(acc);
+  }
 }
 
 // Copies the rows every (chunk, head) list names into list order: qg / dog [R*H, 128] and lse_g / delta_g
@@ -185,14 +253,14 @@ extern "C" int moba_merge_fwd(void* out, float* lse, int32_t dtype, int32_t H, c
   MOBA_SET_DEVICE(device);
   const int64_t n = static_cast<int64_t>(info->total_tokens) * H;
   if (n == 0) return 0;
-  const unsigned grid = static_cast<unsigned>((n + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == MOBA_DTYPE_BF16)
-    merge_fwd_kernel<true><<<grid, 256, 0, st>>>(static_cast<uint16_t*>(out), lse, n, info->kk,
-                                                 static_cast<const uint16_t*>(part_o), part_lse, row_of);
-  else
-    merge_fwd_kernel<false><<<grid, 256, 0, st>>>(static_cast<uint16_t*>(out), lse, n, info->kk,
-                                                  static_cast<const uint16_t*>(part_o), part_lse, row_of);
+  auto run = [&](auto kern) {
+    kern<<<row_grid(n, kern), kRowWarps * 32, 0, st>>>(static_cast<uint16_t*>(out), lse, n, info->kk,
+                                          static_cast<const uint16_t*>(part_o), part_lse, row_of);
+  };
+  const bool bf16 = dtype == MOBA_DTYPE_BF16;
+  if (info->kk <= 2) bf16 ? run(merge_fwd_kernel<true, 2>) : run(merge_fwd_kernel<false, 2>);
+  else bf16 ? run(merge_fwd_kernel<true, 4>) : run(merge_fwd_kernel<false, 4>);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -206,12 +274,13 @@ extern "C" int moba_bwd_delta(const void* out, const void* d_out, int32_t dtype,
   MOBA_SET_DEVICE(device);
   const int64_t n = n_tokens * H;
   if (n == 0) return 0;
-  const unsigned grid = static_cast<unsigned>((n + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == MOBA_DTYPE_BF16)
-    delta_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), n, delta);
+    delta_kernel<true><<<row_grid((n + 3) / 4, delta_kernel<true>), kRowWarps * 32, 0, st>>>(
+        static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), n, delta);
   else
-    delta_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), n, delta);
+    delta_kernel<false><<<row_grid((n + 3) / 4, delta_kernel<false>), kRowWarps * 32, 0, st>>>(
+        static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), n, delta);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -228,12 +297,13 @@ extern "C" int moba_merge_dq(void* dq, int32_t dtype, int32_t H, const moba_plan
   MOBA_SET_DEVICE(device);
   const int64_t n = static_cast<int64_t>(info->total_tokens) * H;
   if (n == 0) return 0;
-  const unsigned grid = static_cast<unsigned>((n + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == MOBA_DTYPE_BF16)
-    merge_dq_kernel<true><<<grid, 256, 0, st>>>(static_cast<uint16_t*>(dq), dq_self, n, info->kk, part_dq, row_of);
-  else
-    merge_dq_kernel<false><<<grid, 256, 0, st>>>(static_cast<uint16_t*>(dq), dq_self, n, info->kk, part_dq, row_of);
+  auto run = [&](auto kern) {
+    kern<<<row_grid(n, kern), kRowWarps * 32, 0, st>>>(static_cast<uint16_t*>(dq), dq_self, n, info->kk, part_dq, row_of);
+  };
+  const bool bf16 = dtype == MOBA_DTYPE_BF16;
+  if (info->kk <= 2) bf16 ? run(merge_dq_kernel<true, 2>) : run(merge_dq_kernel<false, 2>);
+  else bf16 ? run(merge_dq_kernel<true, 4>) : run(merge_dq_kernel<false, 4>);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }

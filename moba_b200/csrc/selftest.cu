@@ -125,7 +125,7 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
           umma_ss(tmem, umma_smem_desc_nosw(smem_u32(sm.x[0]), 128, 256), umma_smem_desc_nosw(smem_u32(sm.x[1]), 128, 256),
                   idesc, 1);
       } else if (mode == 5) {
-        // both operands MN-major, N = 64: C[m, n] = sum_k A[k, m] B[k, n] (the dQ^T = K^T dS^T product of the backward)
+        // both operands MN-major, N = 64: C[m, n] = sum_k A[k, m] B[k, n]
         constexpr uint32_t idesc = umma_idesc(128, 64, kBf16, true, true);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)

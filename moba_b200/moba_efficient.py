@@ -9,8 +9,6 @@ import torch
 from . import ops
 
 _STATUS = {}
-# development switch while the one-pass backward is being validated: True runs the two-kernel backward
-SPLIT_BACKWARD = bool(int(__import__("os").environ.get("MOBA_SPLIT_BACKWARD", "0")))
 
 
 def _status_word(device):
@@ -132,12 +130,8 @@ def _backward(qc, kc, vc, out, d_out, ctx):
     delta = ops.bwd_delta(out, d_out)
     # the rows every (chunk, head) list names, copied into list order once for both backward kernels
     gathered = ops.gather_rows(qc, d_out, plan, ctx.lists, ctx.lse, delta) if plan.kk > 0 else (None,) * 4
-    if SPLIT_BACKWARD:
-        dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
-        dq_self, part_dq = ops.attn_bwd_dq(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
-    else:
-        dk, dv, dq_self, part_dq = ops.attn_bwd(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status,
-                                                gathered=gathered)
+    dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
+    dq_self, part_dq = ops.attn_bwd_dq(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
     dq = ops.merge_dq(dq_self, plan, part_dq, ctx.row_of, qc.dtype)
     return dq, dk, dv
 
@@ -258,11 +252,8 @@ class MixedAttention(torch.autograd.Function):
         if d_out.stride() != qc.stride():
             qc, kc, vc = qc.contiguous(), kc.contiguous(), vc.contiguous()
         delta = ops.bwd_delta(out, d_out)
-        if SPLIT_BACKWARD:
-            dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan_self, none3, lse, delta, status, parts=1)
-            dq_self, _ = ops.attn_bwd_dq(qc, kc, vc, d_out, plan_self, none3, lse, delta, status, parts=1)
-        else:
-            dk, dv, dq_self, _ = ops.attn_bwd(qc, kc, vc, d_out, plan_self, none3, lse, delta, status, parts=1)
+        dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan_self, none3, lse, delta, status, parts=1)
+        dq_self, _ = ops.attn_bwd_dq(qc, kc, vc, d_out, plan_self, none3, lse, delta, status, parts=1)
         dq = dq_self.to(out.dtype)
         R = mq.shape[0]
         if g is None:
@@ -276,12 +267,8 @@ class MixedAttention(torch.autograd.Function):
         delta_g = delta.view(-1).index_select(0, idx)
         do3, lse2, delta2 = dog.view(R, 1, D), lse_g.view(R, 1), delta_g.view(R, 1)
         rows = (mq.view(R, D), dog, lse_g, delta_g)
-        if SPLIT_BACKWARD:
-            dmk, dmv = ops.attn_bwd_dkdv(mq, mk, mv, do3, view, lists, lse2, delta2, status, parts=2, gathered=rows)
-            _, part_dq = ops.attn_bwd_dq(mq, mk, mv, do3, view, lists, lse2, delta2, status, parts=2, gathered=rows)
-        else:
-            dmk, dmv, _, part_dq = ops.attn_bwd(mq, mk, mv, do3, view, lists, lse2, delta2, status, parts=2,
-                                                gathered=rows)
+        dmk, dmv = ops.attn_bwd_dkdv(mq, mk, mv, do3, view, lists, lse2, delta2, status, parts=2, gathered=rows)
+        _, part_dq = ops.attn_bwd_dq(mq, mk, mv, do3, view, lists, lse2, delta2, status, parts=2, gathered=rows)
         dmq = part_dq.to(out.dtype).view(R, 1, D)
         dmkv = torch.stack((dmk, dmv), dim=1)
         return dq, dk, dv, None, dmq, dmkv, None, None, None, None, None

@@ -355,29 +355,6 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
     return dq_self, part_dq
 
 
-def attn_bwd(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None):
-    """The whole tile backward in one pass: (dk, dv [S_k, H_kv, D], dq_self [S,H,D] fp32, part_dq [R*H, D] fp32).
-    `gathered` = (qg, dog, lse_g, delta_g), the rows in list order (gather_rows); produced here when not given."""
-    S, H, D = q.shape
-    kv = _kv_layout(q, k, v)
-    list_off, work_off, list_tok = lists
-    if gathered is None:
-        gathered = gather_rows(q, d_out, plan, lists, lse, delta) if (parts & 2 and plan.kk > 0) else (None,) * 4
-    qg, dog, lse_g, delta_g = gathered
-    dk = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
-    dq_self = torch.empty((S, H, D), dtype=torch.float32, device=q.device) if parts & 1 else None
-    part_dq = torch.empty((max(plan.rows_total(H), 1), D), dtype=torch.float32, device=q.device)
-    turn = torch.empty(max(_lib.lib.moba_attn_bwd_ws_ints(ctypes.byref(plan.info), H), 1), dtype=torch.int32,
-                       device=q.device)
-    with _timed("attn_bwd", q.device):
-        call("moba_attn_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0), q.stride(1),
-             kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(qg), _ptr(dog),
-             _ptr(lse_g), _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dk), _ptr(dv), _ptr(dq_self), _ptr(part_dq),
-             _ptr(turn), parts, _ptr(status), _dev_index(q), _stream(q.device))
-    return dk, dv, dq_self, part_dq
-
-
 def merge_dq(dq_self, plan, part_dq, row_of, dtype):
     """dq [S,H,D] in `dtype`: fp32 sum of the self piece and the gathered pieces, rounded once."""
     S, H, D = dq_self.shape

@@ -36,9 +36,31 @@ class Layout:
         self.seq_chunk0 = torch.tensor(first, device=dev)[seq]
 
 
-def reference_selection(q, k, lay, topk, rep=1):
+def check_pooled_keys(kmean_kernel, k, lay):
+    """The kernel's pooled keys [n_chunks, H_kv, D] (fp32 holding values of k.dtype) against torch's .mean() of the
+    full chunks: the same fp32 sum up to its order, so an entry may differ by one rounding step of k.dtype where
+    the sum falls next to a rounding boundary -- rarely (< 1e-3 of the entries)."""
+    c = 0
+    n_bad = n_all = 0
+    for b, (t0, t1) in enumerate(zip(lay.cu, lay.cu[1:])):
+        nc = lay.n_local[b] - 1
+        if nc > 0:
+            want = k[t0:t0 + nc * lay.chunk].view(nc, lay.chunk, k.shape[1], k.shape[2]).mean(dim=1).float()
+            got = kmean_kernel[c:c + nc]
+            ulp = 2.0 ** -7 if k.dtype == torch.bfloat16 else 2.0 ** -10
+            assert bool(((got - want).abs() <= ulp * want.abs().clamp(min=2.0 ** -20)).all())
+            n_bad += int((got != want).sum())
+            n_all += want.numel()
+        c += lay.n_local[b]
+    assert n_bad <= 1e-3 * max(n_all, 1), (n_bad, n_all)
+
+
+def reference_selection(q, k, lay, topk, rep=1, kmean_kernel=None):
     """mask [S, H, n_max] bool over LOCAL chunk ids, and the fp32 gate [S, H, n_max] (-inf where not a
-    candidate). k may carry H / rep heads (query head h reads key head h // rep)."""
+    candidate). k may carry H / rep heads (query head h reads key head h // rep). With kmean_kernel (the pooling
+    kernel's output, checked by check_pooled_keys) the gate is evaluated on exactly the pooled keys the gate kernel
+    saw: a pooled key that rounds the other way on a half-ulp tie moves a score by ~1e-3 absolute, which is not
+    what the selection comparison is about."""
     S, Hq, D = q.shape
     dev = q.device
     mask = torch.zeros((S, Hq, lay.n_max), dtype=torch.bool, device=dev)
@@ -49,7 +71,11 @@ def reference_selection(q, k, lay, topk, rep=1):
         if n_b <= 1:
             continue
         nc = n_b - 1                                                  # candidate chunks: all full-size
-        kmean = k[t0:t0 + nc * B].view(nc, B, k.shape[1], D).mean(dim=1).float()       # rounded to k.dtype first
+        if kmean_kernel is not None:
+            c0 = sum(lay.n_local[:b])
+            kmean = kmean_kernel[c0:c0 + nc].float()
+        else:
+            kmean = k[t0:t0 + nc * B].view(nc, B, k.shape[1], D).mean(dim=1).float()   # rounded to k.dtype first
         if rep > 1:
             kmean = kmean.repeat_interleave(rep, dim=1)
         for h0 in range(0, Hq, 4):                                    # a few heads at a time bounds the memory
@@ -114,13 +140,13 @@ def check_query_rows(rows, q, k, v, d_out, out, dq, mask, lay, rep=1):
         sc = (kf @ q[s_i, h_i].float()) * scale
         p = torch.softmax(sc, 0)
         o_ref = p @ vf
-        H.assert_parity(f"out[{s_i},{h_i}]", out[s_i, h_i].float().cpu().numpy(), o_ref.cpu().numpy())
+        H.assert_row_parity(f"out[{s_i},{h_i}]", out[s_i, h_i].float().cpu().numpy(), o_ref.cpu().numpy())
         if dq is not None:
             do = d_out[s_i, h_i].float()
             dp = vf @ do
             delta = (do * o_ref).sum()
             dq_ref = ((p * (dp - delta)) * scale) @ kf
-            H.assert_parity(f"dq[{s_i},{h_i}]", dq[s_i, h_i].float().cpu().numpy(), dq_ref.cpu().numpy())
+            H.assert_row_parity(f"dq[{s_i},{h_i}]", dq[s_i, h_i].float().cpu().numpy(), dq_ref.cpu().numpy())
 
 
 def _lse_of(qs, h_i, q, k, mask, lay, hk):
@@ -171,8 +197,8 @@ def check_key_rows(rows, q, k, v, d_out, out, dk, dv, mask, lay, rep=1):
             delta = (dof * of).sum(-1)
             dk_ref += ((p * (dof @ v[t_i, hk].float() - delta)) * scale) @ qf
         # the bound grows with the number of rounded summands (one per query head of the group)
-        H.assert_parity(f"dv[{t_i},{hk}]", dv[t_i, hk].float().cpu().numpy() / rep ** 0.5, dv_ref.cpu().numpy() / rep ** 0.5)
-        H.assert_parity(f"dk[{t_i},{hk}]", dk[t_i, hk].float().cpu().numpy() / rep ** 0.5, dk_ref.cpu().numpy() / rep ** 0.5)
+        H.assert_row_parity(f"dv[{t_i},{hk}]", dv[t_i, hk].float().cpu().numpy() / rep ** 0.5, dv_ref.cpu().numpy() / rep ** 0.5)
+        H.assert_row_parity(f"dk[{t_i},{hk}]", dk[t_i, hk].float().cpu().numpy() / rep ** 0.5, dk_ref.cpu().numpy() / rep ** 0.5)
 
 
 def check_lists(plan, heads, sel, list_off, work_off, list_tok, row_of):

@@ -87,10 +87,12 @@ def test_varlen_training_batch_two_head_cut(cuda_device):
     check_kernel_status(dev)
 
     lay = R.Layout(cu, chunk, dev)
-    ref_mask, gate = R.reference_selection(q, k, lay, topk)
     plan = ops.get_plan(cu, chunk, topk, dev)
     assert plan.info.n_chunks == 1231
-    sel, _, tile_cnt = ops.gate_topk(q, ops.pool_keys(k, plan), plan)
+    kmean = ops.pool_keys(k, plan)
+    R.check_pooled_keys(kmean, k, lay)
+    ref_mask, gate = R.reference_selection(q, k, lay, topk, kmean_kernel=kmean)
+    sel, _, tile_cnt = ops.gate_topk(q, kmean, plan)
     got_mask = R.kernel_selection(sel, lay)
     R.assert_same_selection(got_mask, ref_mask, gate, lay, topk)
     list_off, work_off, list_tok, row_of = ops.build_lists(plan, heads, sel, tile_cnt)
@@ -124,9 +126,11 @@ def test_one_million_token_prefill_share(cuda_device):
     check_kernel_status(dev)
     lay = R.Layout(cu, chunk, dev)
     plan = ops.get_plan(cu, chunk, topk, dev)
-    sel, _, tile_cnt = ops.gate_topk(q, ops.pool_keys(k, plan), plan)
+    kmean = ops.pool_keys(k, plan)
+    R.check_pooled_keys(kmean, k, lay)
+    sel, _, tile_cnt = ops.gate_topk(q, kmean, plan)
     got_mask = R.kernel_selection(sel, lay)
-    ref_mask, gate = R.reference_selection(q, k, lay, topk, rep=heads)
+    ref_mask, gate = R.reference_selection(q, k, lay, topk, rep=heads, kmean_kernel=kmean)
     R.assert_same_selection(got_mask, ref_mask, gate, lay, topk)
     del ref_mask, gate
     list_off, work_off, list_tok, row_of = ops.build_lists(plan, heads, sel, tile_cnt)
@@ -167,9 +171,11 @@ def test_128k_layer_grouped_query_mapping(cuda_device):
 
     lay = R.Layout(cu, chunk, dev)
     plan = ops.get_plan(cu, chunk, topk, dev)
-    sel, _, _ = ops.gate_topk(q, ops.pool_keys(k, plan), plan)
+    kmean = ops.pool_keys(k, plan)
+    R.check_pooled_keys(kmean, k, lay)
+    sel, _, _ = ops.gate_topk(q, kmean, plan)
     got_mask = R.kernel_selection(sel, lay)
-    ref_mask, gate = R.reference_selection(q, k, lay, topk, rep=rep)
+    ref_mask, gate = R.reference_selection(q, k, lay, topk, rep=rep, kmean_kernel=kmean)
     R.assert_same_selection(got_mask, ref_mask, gate, lay, topk)
     del ref_mask, gate
     rng = np.random.RandomState(6)

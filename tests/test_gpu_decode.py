@@ -1,5 +1,5 @@
 """Decode-phase dense attention (moba_decode_attn behind moba_layer's q_len != kv_len branch, the stand-in for the
-flash_attn_func call of moba/wrapper.py:76-82) against the CPU oracle."""
+flash_attn_func call of moba/wrapper.py:76-82) against the CPU oracle, and both against flash_attn_func itself."""
 import numpy as np
 import pytest
 import torch
@@ -93,3 +93,32 @@ def test_decode_argument_errors(cuda_device):
     k1 = torch.zeros(1, 2, 1, 128, dtype=torch.bfloat16, device=cuda_device)
     with pytest.raises(Exception):
         ops.decode_attn(q, k1, k1)                 # fewer keys than query positions
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk,dtype", [
+    (1, 4, 1, 1, 1000, "bf16"), (2, 8, 2, 1, 4096, "bf16"), (2, 4, 4, 3, 517, "bf16"), (1, 8, 1, 5, 300, "f16"),
+    (1, 2, 2, 7, 7, "bf16"), (1, 32, 8, 1, 20000, "bf16"),
+])
+def test_decode_oracle_and_kernel_against_flash_attn_func(cuda_device, B, Hq, Hkv, Lq, Lk, dtype):
+    """Pins the decode branch to the call the reference makes there: flash_attn_func(query, key, value, dropout,
+    scaling, True) on [batch, len, heads, dim] tensors (moba/wrapper.py:79-82), run here on the installed flash-attn.
+    Both the numpy restatement (oracle.decode_attention) and the kernel are compared with its output. Skips when
+    flash-attn cannot run on this GPU."""
+    from moba_b200 import ops
+
+    try:
+        from flash_attn import flash_attn_func
+    except ImportError:
+        pytest.skip("flash-attn is not installed")
+    (q, k, v), (tq, tk, tv) = _inputs(9, B, Hq, Hkv, Lq, Lk, dtype, cuda_device)
+    scale = 128 ** -0.5
+    try:
+        ref = flash_attn_func(tq.transpose(1, 2), tk.transpose(1, 2), tv.transpose(1, 2), 0.0, scale, True)
+        torch.cuda.synchronize()
+    except RuntimeError as e:
+        pytest.skip(f"flash-attn cannot run here: {str(e).splitlines()[0]}")
+    ref = t2n(ref)                                                   # [B, Lq, Hq, 128]
+    want = orc.decode_attention(q, k, v, scale, dtype)
+    assert np.abs(want - ref).max() < 1e-2 and np.abs(want - ref).mean() < 5e-4      # the oracle restates that call
+    got = t2n(ops.decode_attn(tq, tk, tv, scale))
+    H.assert_parity("kernel vs flash_attn_func", got, ref)

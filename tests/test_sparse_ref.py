@@ -27,7 +27,7 @@ def test_sparse_ref_reproduces_the_oracle(monkeypatch):
     def tight(name, got, want):
         assert np.abs(np.asarray(got) - np.asarray(want)).max() < 2e-4, name
 
-    monkeypatch.setattr(H, "assert_parity", tight)
+    monkeypatch.setattr(H, "assert_row_parity", tight)
     rows = [(s, h) for s in (0, 127, 128, 299, 300, 301, 700, 1099, 1100, 1499) for h in range(heads)]
     to = lambda x: torch.from_numpy(np.ascontiguousarray(x))
     R.check_query_rows(rows, tq, tk, tv, tdo, to(out), to(dq), mask, lay)
