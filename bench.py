@@ -330,6 +330,10 @@ def run_ours(args, cfg_id, cfg):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # the pinned host buffers of the end-to-end leg should sit on the GPU's NUMA node (one process per GPU)
+    from moba_b200.host_io import bind_host_to_device_numa
+
+    numa_node = None if args.no_numa_bind else bind_host_to_device_numa(dev)
     if world > 1:
         # keep stdout to the one JSON line: NCCL's version / info banner goes to a file instead
         os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), "nccl_debug.%h.%p.log"))
@@ -423,18 +427,20 @@ def run_ours(args, cfg_id, cfg):
 
         out_dev = torch.empty((S, hl, D), dtype=torch.bfloat16, device=dev) if world > 1 else None
 
-        def e2e_step():
+        copy_stats = {}
+
+        def e2e_step(stats=None):
             # host tensors in, host tensors out, through the package's host entry point: head groups are
             # pipelined so that the H2D / D2H copies of one group overlap with the kernels of another
             moba_attn_varlen_host(hq, hk, hv, cu, max(cfg["lens"]), cfg["chunk"], cfg["topk"],
                                   d_out=hdo if cfg["backward"] else None, out=ho,
                                   grads=tuple(hgrads) if cfg["backward"] else None, head_groups=args.head_groups,
-                                  device=dev, out_device=out_dev)
+                                  device=dev, out_device=out_dev, stats=stats)
             if world > 1:
                 dist.all_gather_into_tensor(out_all, out_dev)
 
         e2e_steps = max(1, min(args.steps, 3))
-        e2e_step()
+        e2e_step(copy_stats)          # untimed first call, with the per-slice copy rates recorded
         barrier()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s0.record()
@@ -449,6 +455,12 @@ def run_ours(args, cfg_id, cfg):
         nbytes = hq.numel() * 2
         e2e = dict(ms=e2e_ms, h2d=4 * nbytes if cfg["backward"] else 3 * nbytes,
                    d2h=(4 if cfg["backward"] else 1) * nbytes)
+        if copy_stats:
+            def rate(key):
+                return [round(b / ms / 1e6, 1) if ms > 0 else None for b, ms in copy_stats[key]]
+
+            e2e["copy_rates"] = {"head_slices": copy_stats["slices"], "h2d_gbs_per_slice": rate("h2d"),
+                                 "d2h_gbs_per_slice": rate("d2h"), "host_numa_node": numa_node}
     check_kernel_status(dev)
 
     # ---- checksums (outside every timed region): equal bits at every N ---------------------------------
@@ -522,6 +534,8 @@ def run_ours(args, cfg_id, cfg):
         if e2e:
             line["e2e"] = {"value": flops / (e2e["ms"] * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e["ms"],
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
+            if "copy_rates" in e2e:
+                line["e2e"]["copy_rates_rank0"] = e2e["copy_rates"]
         emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -643,6 +657,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--head-groups", type=int, default=8, help="head slices pipelined in the end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-numa-bind", action="store_true", help="leave the process's CPU affinity alone")
     ap.add_argument("--no-secondary", action="store_true", help="skip the 1M-token forward-only line (config 3 runs)")
     args = ap.parse_args()
     claim_stdout()

@@ -127,7 +127,8 @@ typedef struct moba_kv_layout {
  * Gate: fp32 score q . kmean for every causal candidate chunk of the query's own sequence, top-kk per
  * (token, head). Replaces the einsum, masks and torch.topk of moba/moba_efficient.py:341-371 without the
  * dense [F, H, S] tensors.
- *   sel      [S, H, kk] int32: global chunk ids chosen, best first, -1 where a query has fewer candidates
+ *   sel      [S, H, kk] int32: global chunk ids chosen (in ascending chunk order from the tensor-pipe kernel for
+ *            sequences of up to 257 chunks, best first otherwise), then -1 where a query has fewer candidates
  *   sel_score[S, H, kk] fp32 (may be NULL): their scores
  *   tile_cnt [cand_per_head * H] int32: per (query tile, head, candidate) selection counts (input of
  *            moba_build_lists)

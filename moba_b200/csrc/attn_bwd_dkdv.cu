@@ -318,7 +318,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       while (g >= sm.seg_start[seg + 1]) ++seg;
       const int st = g & (kStages - 1), h = g & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_q_full[st], (g >> 2) & 1, wctx) && mbar_wait(&sm.bar_s_ready[h], (g >> 1) & 1, wctx));
-      if (!ok) break;
+      if (!ok) {
+        // the partner warp may have seen the barrier complete and be waiting at the pair barrier: release it
+        asm volatile("bar.arrive %0, 64;" ::"r"(pair_bar) : "memory");
+        break;
+      }
       tc_fence_after_sync();
       // the first own-chunk tile of every head's segment is the diagonal one: key <= query
       const bool diag = n_self > 0 && g - sm.seg_start[seg] < 2;

@@ -272,7 +272,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       const BarPhase need[2] = {{&sm.bar_s_ready[b], static_cast<uint32_t>((j >> 1) & 1)},
                                 {&sm.bar_dp_ready, static_cast<uint32_t>(j & 1)}};
       ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
-      if (!ok) break;
+      if (!ok) {
+        // warps of the lane quarter that saw the barriers complete may be waiting at the quarter's barrier: release them
+        asm volatile("bar.arrive %0, 128;" ::"r"(quad_bar) : "memory");
+        break;
+      }
       tc_fence_after_sync();
       int ncol = nkeys - j * MOBA_TILE;                            // keys of this tile that exist
       if constexpr (!kGathered) ncol = min(ncol, first + row - key0 - j * MOBA_TILE + 1);   // causal: key <= query

@@ -41,10 +41,6 @@ constexpr int kSoftmaxWarps = 8;
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
 constexpr int kTmemCols = 256;
 constexpr float kRescaleThreshold = 8.0f;
-#ifndef MOBA_FWD_POLY
-#define MOBA_FWD_POLY 3
-#endif
-constexpr int kPolyLane = MOBA_FWD_POLY;      // which of every four column pairs takes the polynomial exp2 (-1: none)
 
 
 struct __align__(1024) FwdSmem {
@@ -261,7 +257,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_s_ready, j & 1, wctx));
-      if (!ok) break;
+      if (!ok) {
+        // the partner warp may have seen the barrier complete and be waiting at the pair barrier: release it
+        asm volatile("bar.arrive %0, 64;" ::"r"(pair_bar) : "memory");
+        break;
+      }
       tc_fence_after_sync();
       const bool last = j == nkv - 1;
       int ncol = nkeys - j * MOBA_TILE;                       // keys of this tile that exist
@@ -286,9 +286,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             for (int c = 0; c < 16; ++c) {
               const float s0 = __uint_as_float(s[2 * c]), s1 = __uint_as_float(s[2 * c + 1]);
               if (with_max) mx = fmaxf(mx, fmaxf(s0, s1));
-              // a quarter of the exponentials run on the FMA pipe: the exp2 unit is as busy as the tensor pipe here
-              const float p0 = (c & 3) == kPolyLane ? ex2_poly(fmaf(s0, sc, -m_used)) : ex2_approx(fmaf(s0, sc, -m_used));
-              const float p1 = (c & 3) == kPolyLane ? ex2_poly(fmaf(s1, sc, -m_used)) : ex2_approx(fmaf(s1, sc, -m_used));
+              const float p0 = ex2_approx(fmaf(s0, sc, -m_used));
+              const float p1 = ex2_approx(fmaf(s1, sc, -m_used));
               ls0 += p0;
               ls1 += p1;
               pk[h * 16 + c] = pack2<kBf16>(p0, p1);
@@ -322,7 +321,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         if (j > 0) {
           // O may still be accumulating P V of the previous tile
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_pv_done, (j - 1) & 1, wctx));
-          if (!ok) break;
+          if (!ok) {
+            // the partner warp may have seen the barrier complete and be waiting at the pair barrier: release it
+            asm volatile("bar.arrive %0, 64;" ::"r"(pair_bar) : "memory");
+            break;
+          }
           tc_fence_after_sync();
 #pragma unroll
           for (int i = 0; i < 2; ++i) {

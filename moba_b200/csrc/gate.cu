@@ -237,7 +237,7 @@ offsets_kernel(int E, int32_t* __restrict__ list_off, int32_t* __restrict__ work
 __global__ void __launch_bounds__(128)
 fill_lists_kernel(int H, PlanDev plan, const int32_t* __restrict__ sel, const int32_t* __restrict__ tile_cnt,
                   const int32_t* __restrict__ list_off, int32_t* __restrict__ list_tok,
-                  int32_t* __restrict__ row_of, int* status) {
+                  int32_t* __restrict__ row_of, int* status, int n_rows_total) {
   extern __shared__ __align__(16) uint8_t fill_smem[];
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(fill_smem);
   const int tile = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -276,7 +276,13 @@ fill_lists_kernel(int H, PlanDev plan, const int32_t* __restrict__ sel, const in
       int rank = __popc(bitmap[lc * 4 + warp] & lt);
       for (int w = 0; w < warp; ++w) rank += __popc(bitmap[lc * 4 + w]);
       r = list_off[g * H + h] + tile_cnt[cnt0 + lc] + rank;
-      list_tok[r] = tok;
+      // counts that do not belong to this selection (a gate launch that was cut short) must not become an address
+      if (r < 0 || r >= n_rows_total) {
+        if (status) atomicCAS(status, 0, 2);
+        r = -1;
+      } else {
+        list_tok[r] = tok;
+      }
     }
     row_of[slot0 + j] = r;
   }
@@ -362,7 +368,8 @@ extern "C" int moba_build_lists(int32_t H, const moba_plan_info* info, const int
   const size_t smem = static_cast<size_t>(info->max_cand > 0 ? info->max_cand : 1) * 16;
   MOBA_CUDA_OK(cudaFuncSetAttribute(fill_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(plan.n_qtiles, H);
-  fill_lists_kernel<<<grid, 128, smem, st>>>(H, plan, sel, tile_cnt, list_off, list_tok, row_of, status);
+  fill_lists_kernel<<<grid, 128, smem, st>>>(H, plan, sel, tile_cnt, list_off, list_tok, row_of, status,
+                                             static_cast<int>(info->rows_per_head * H));
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }

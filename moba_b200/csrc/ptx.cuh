@@ -336,19 +336,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA and integer pipes instead of the exp2 unit (16 results per clock and SM, which a 128 x 128 tile's
-// softmax saturates): x = n + r with n = round(x), |r| <= 0.5; 2^r by a cubic fitted for the smallest relative
-// error on [-0.5, 0.5] (7.5e-5, far below one rounding step of a 16-bit probability); 2^n by adding n to the
-// exponent field. Valid for x <= 127; x < -126 gives ~2^-126.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float xf = x + 12582912.0f;                 // 1.5 * 2^23: n sits in the low mantissa bits
-  const float r = x - (xf - 12582912.0f);
-  float p = fmaf(0.05517083778977394f, r, 0.24260935187339783f);
-  p = fmaf(p, r, 0.6932609677314758f);
-  p = fmaf(p, r, 0.9999281764030457f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
-}
 // pack two fp32 into one 32-bit word of two 16-bit floats; `lo` lands in the low half.
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

@@ -22,8 +22,36 @@ def _pinned(t, name):
         raise ValueError(f"{name} must be in pinned host memory (tensor.pin_memory()) for asynchronous copies")
 
 
+def bind_host_to_device_numa(device):
+    """Restricts the calling process to the CPUs of the NUMA node the GPU hangs off (read from sysfs), so that the
+    pinned host buffers it allocates afterwards and the copy threads sit next to the GPU's PCIe root: with one
+    process per GPU on a two-socket host, half the processes otherwise stream their tensors across the socket
+    interconnect. Returns the node number, or None when the topology cannot be read (nothing is changed then)."""
+    import os
+
+    try:
+        props = torch.cuda.get_device_properties(torch.device(device))
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, d_out=None, out=None,
-                          grads=None, head_groups=4, device=None, out_device=None):
+                          grads=None, head_groups=4, device=None, out_device=None, stats=None):
     """MoBA attention (and, with d_out, its backward) on pinned host tensors [seqlen, head, head_dim].
 
     Args:
@@ -36,6 +64,8 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
             with more than one, the first and the last slice are additionally cut down to one key/value head
         out_device: optional device tensor [seqlen, head, head_dim] that also receives the output (e.g. to feed
             a collective); written on the current stream
+        stats: optional dict; receives "h2d" and "d2h", lists of (bytes, milliseconds) per head slice measured with
+            events on the two copy streams (the achieved copy rates of the slices)
     Returns:
         out, or (out, (dq, dk, dv)) when d_out is given. The results are complete when this function returns.
     """
@@ -77,14 +107,24 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
               for kv in is_kv[:len(srcs)]] for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(groups)]
     ev_done = [torch.cuda.Event() for _ in range(groups)]
+    timed = stats is not None
+    t_in = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)] if timed else None
+    t_out = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)] if timed else None
+    n_in = [0] * groups
+    n_out = [0] * groups
 
     def copy_in(g):
         with torch.cuda.stream(s_in):
             if g >= 2:
                 s_in.wait_event(ev_done[g - 2])          # the staging set is free again
+            if timed:
+                t_in[g][0].record(s_in)
             for dst, src, kv in zip(stage[g % 2], srcs, is_kv):
                 h0, h1 = (kv_bounds[g], kv_bounds[g + 1]) if kv else (bounds[g], bounds[g + 1])
                 ops.copy_heads(dst[:, : h1 - h0], src[:, h0:h1], s_in)
+                n_in[g] += S * (h1 - h0) * D * src.element_size()
+            if timed:
+                t_in[g][1].record(s_in)
             ev_in[g].record(s_in)
 
     copy_in(0)
@@ -110,12 +150,21 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
         ev_done[g].record(compute)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[g])
+            if timed:
+                t_out[g][0].record(s_out)
             for dst, src, a, b in results:
                 src.record_stream(s_out)
                 ops.copy_heads(dst[:, a:b], src if src.is_contiguous() else src.contiguous(), s_out)
+                n_out[g] += src.numel() * src.element_size()
+            if timed:
+                t_out[g][1].record(s_out)
     compute.wait_stream(s_out)
     compute.wait_stream(s_in)
     for buf in stage[0] + stage[1]:
         buf.record_stream(s_in)
     torch.cuda.current_stream(device).synchronize()
+    if timed:
+        stats["h2d"] = [(n_in[g], t_in[g][0].elapsed_time(t_in[g][1])) for g in range(groups)]
+        stats["d2h"] = [(n_out[g], t_out[g][0].elapsed_time(t_out[g][1])) for g in range(groups)]
+        stats["slices"] = [b - a for a, b in zip(bounds, bounds[1:])]
     return (out, grads) if backward else out
