@@ -78,8 +78,9 @@ def _share_strides(q, k, v):
     return q.contiguous(), k.contiguous(), v.contiguous()
 
 
-def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk):
-    """Runs pool -> gate/top-k -> lists -> attention tiles -> merge. Returns (out in q.dtype, context)."""
+def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, out=None):
+    """Runs pool -> gate/top-k -> lists -> attention tiles -> merge. Returns (out in q.dtype, context). `out`:
+    optional contiguous [S, H, D] buffer of the compute dtype that receives the result."""
     if k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2] or k.shape[1] < 1 \
             or q.shape[1] % k.shape[1] != 0:
         raise ValueError("k and v must have the shape of q, or the same shape with a head count that divides "
@@ -111,28 +112,31 @@ def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk):
         longest = max((b - a for a, b in zip(plan.cu_host, plan.cu_host[1:])), default=1)
         plan = ops.Plan(plan.cu_host, max(longest, 1), 1, dev)
     qc, kc, vc = _share_strides(_as_compute(q), _as_compute(k), _as_compute(v))
-    out, lse, part_o, part_lse = ops.attn_fwd(qc, kc, vc, plan, lists, status)
+    out, lse, part_o, part_lse = ops.attn_fwd(qc, kc, vc, plan, lists, status, out=out)
     if plan.kk > 0:
         ops.merge_fwd(out, lse, plan, part_o, part_lse, row_of)
     ctx.plan, ctx.lists, ctx.row_of, ctx.lse = plan, lists, row_of, lse
     return out, (qc, kc, vc), ctx
 
 
-def _backward(qc, kc, vc, out, d_out, ctx):
+def _backward(qc, kc, vc, out, d_out, ctx, grads_out=None):
     """dq, dk, dv in the compute dtype. No gradient flows through the selection
-    (moba/moba_efficient.py:365-371 uses indices / booleans only)."""
+    (moba/moba_efficient.py:365-371 uses indices / booleans only). `grads_out`: optional contiguous (dq [S,H,D],
+    dk, dv [S,H_kv,D]) buffers that receive the gradients."""
     status = _status_word(qc.device)
     plan = ctx.plan
     d_out = d_out if d_out.dtype == out.dtype else d_out.to(out.dtype)
     d_out = d_out.contiguous()
-    if d_out.stride() != qc.stride():
-        qc, kc, vc = qc.contiguous(), kc.contiguous(), vc.contiguous()
     delta = ops.bwd_delta(out, d_out)
+    if d_out.stride() != qc.stride():
+        # the tile kernels read d_out through q's strides: one strided copy of d_out, not three of q / k / v
+        d_out = torch.empty_strided(qc.shape, qc.stride(), dtype=d_out.dtype, device=d_out.device).copy_(d_out)
     # the rows every (chunk, head) list names, copied into list order once for both backward kernels
     gathered = ops.gather_rows(qc, d_out, plan, ctx.lists, ctx.lse, delta) if plan.kk > 0 else (None,) * 4
-    dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
+    dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered,
+                               out=grads_out[1:] if grads_out else None)
     dq_self, part_dq = ops.attn_bwd_dq(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
-    dq = ops.merge_dq(dq_self, plan, part_dq, ctx.row_of, qc.dtype)
+    dq = ops.merge_dq(dq_self, plan, part_dq, ctx.row_of, qc.dtype, out=grads_out[0] if grads_out else None)
     return dq, dk, dv
 
 
@@ -154,6 +158,62 @@ class _MobaAttnFunction(torch.autograd.Function):
         if ctx.in_dtype != dq.dtype:
             dq, dk, dv = dq.to(ctx.in_dtype), dk.to(ctx.in_dtype), dv.to(ctx.in_dtype)
         return dq, dk, dv, None, None, None
+
+
+class _MobaLayerFunction(torch.autograd.Function):
+    """moba_attn_varlen for a batch of equal-length sequences in the memory layout HuggingFace hands to an attention
+    function, [batch, heads, len, dim] (contiguous: what a key/value cache returns), without the permute + reshape
+    copies of moba/wrapper.py:56-58: sequences are independent in MoBA, so every batch element is one call on
+    [len, heads, dim] views of the caller's tensors (strides dim and len * dim), writing straight into the packed
+    [batch * len, heads, dim] output; the gradients land in [batch, len, heads, dim] buffers that are returned as
+    [batch, heads, len, dim] views."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, moba_chunk_size, moba_topk):
+        B, H, S, D = query.shape
+        Hkv = key.shape[1]
+        dt = _compute_dtype(query)
+        out = torch.empty((B * S, H, D), dtype=dt, device=query.device)
+        cu = [0, S]
+        saved, ctxs = [], []
+        for b in range(B):
+            o, (qc, kc, vc), c = _forward(query[b].transpose(0, 1), key[b].transpose(0, 1), value[b].transpose(0, 1),
+                                          cu, moba_chunk_size, moba_topk, out=out[b * S:(b + 1) * S])
+            saved += [qc, kc, vc]
+            ctxs.append(c)
+        ctx.save_for_backward(out, *saved)
+        ctx.moba = ctxs
+        ctx.shape = (B, H, Hkv, S, D)
+        ctx.in_dtype = query.dtype
+        return out if dt == query.dtype else out.to(query.dtype)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        out, *saved = ctx.saved_tensors
+        B, H, Hkv, S, D = ctx.shape
+        dq = torch.empty((B, S, H, D), dtype=out.dtype, device=out.device)
+        dk = torch.empty((B, S, Hkv, D), dtype=out.dtype, device=out.device)
+        dv = torch.empty((B, S, Hkv, D), dtype=out.dtype, device=out.device)
+        for b in range(B):
+            qc, kc, vc = saved[3 * b:3 * b + 3]
+            _backward(qc, kc, vc, out[b * S:(b + 1) * S], d_out[b * S:(b + 1) * S], ctx.moba[b],
+                      grads_out=(dq[b], dk[b], dv[b]))
+        grads = [g.permute(0, 2, 1, 3) for g in (dq, dk, dv)]
+        if ctx.in_dtype != out.dtype:
+            grads = [g.to(ctx.in_dtype) for g in grads]
+        return grads[0], grads[1], grads[2], None, None
+
+
+def moba_attn_batched(query, key, value, moba_chunk_size, moba_topk):
+    """MoBA attention of [batch, heads, len, dim] tensors (equal-length sequences, grouped-query key / value heads
+    allowed) -> [batch * len, heads, dim], reading the tensors in place whatever their strides (innermost stride 1).
+    Used by moba_layer when the reference's hf_to_fa reshape would have to copy."""
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not isinstance(t, torch.Tensor) or t.dim() != 4:
+            raise ValueError(f"{name} must be a [batch, heads, len, head_dim] tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} is on {t.device}: moba_b200 runs on CUDA (sm_100a) only and has no CPU fallback")
+    return _MobaLayerFunction.apply(query, key, value, int(moba_chunk_size), int(moba_topk))
 
 
 def _host_list(t):

@@ -262,16 +262,20 @@ def build_lists(plan, H, sel, tile_cnt, status=None):
     return list_off, work_off, list_tok, row_of
 
 
-def attn_fwd(q, k, v, plan, lists, status, parts=3):
+def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None):
     """Self-chunk causal attention -> (out, lse); gathered rows -> (part_o, part_lse).
 
-    parts: 3 both, 1 own-chunk part only, 2 list part only (buffers of the other part are left unwritten)."""
+    parts: 3 both, 1 own-chunk part only, 2 list part only (buffers of the other part are left unwritten).
+    out: optional contiguous [S, H, D] tensor to receive the result (allocated when None)."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _check_shd(n, t)
     S, H, D = q.shape
     kv = _kv_layout(q, k, v)
     list_off, work_off, list_tok = lists
-    out = torch.empty((S, H, D), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((S, H, D), dtype=q.dtype, device=q.device)
+    elif out.shape != (S, H, D) or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [S, H, D] tensor of q's dtype")
     lse = torch.empty((S, H), dtype=torch.float32, device=q.device)
     R = max(plan.rows_total(H), 1)
     part_o = torch.empty((R, D), dtype=q.dtype, device=q.device)
@@ -316,7 +320,7 @@ def gather_rows(q, d_out, plan, lists, lse, delta):
     return qg, dog, lse_g, delta_g
 
 
-def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None):
+def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, out=None):
     """dk, dv [S_k, H_kv, D] (summed over the query heads that share a key/value head). `gathered` = (qg, dog,
     lse_g, delta_g) when the caller already holds the rows in list order (else they are produced here by
     gather_rows)."""
@@ -326,8 +330,11 @@ def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gath
     if gathered is None:
         gathered = gather_rows(q, d_out, plan, lists, lse, delta) if (parts & 2 and plan.kk > 0) else (None,) * 4
     qg, dog, lse_g, delta_g = gathered
-    dk = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
+    if out is not None:
+        dk, dv = out              # contiguous [S_k, H_kv, D] buffers of the caller
+    else:
+        dk = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((k.shape[0], k.shape[1], D), dtype=q.dtype, device=q.device)
     with _timed("attn_bwd_dkdv", q.device):
         call("moba_attn_bwd_dkdv", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0),
              q.stride(1), kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(qg), _ptr(dog), _ptr(lse_g),
@@ -355,10 +362,10 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
     return dq_self, part_dq
 
 
-def merge_dq(dq_self, plan, part_dq, row_of, dtype):
+def merge_dq(dq_self, plan, part_dq, row_of, dtype, out=None):
     """dq [S,H,D] in `dtype`: fp32 sum of the self piece and the gathered pieces, rounded once."""
     S, H, D = dq_self.shape
-    dq = torch.empty((S, H, D), dtype=dtype, device=dq_self.device)
+    dq = out if out is not None else torch.empty((S, H, D), dtype=dtype, device=dq_self.device)
     with _timed("merge_dq", dq.device):
         call("moba_merge_dq", _ptr(dq), _DTYPES[dtype], H, ctypes.byref(plan.info), _ptr(dq_self), _ptr(part_dq),
              _ptr(row_of), _dev_index(dq), _stream(dq.device))

@@ -11,6 +11,13 @@ def hf_to_fa(x: torch.Tensor):
     return x.permute(0, 2, 1, 3).reshape(-1, x.shape[1], x.shape[3])
 
 
+def _reshape_is_view(x: torch.Tensor) -> bool:
+    """Whether hf_to_fa(x) is a view of x (no copy): true for transposed views of [batch, len, heads, dim] memory."""
+    b, h, s, d = x.shape
+    st = x.permute(0, 2, 1, 3).stride()                 # strides of [batch, len, heads, dim]
+    return b == 1 or st[0] == s * st[1]                 # batch and len merge into one dimension
+
+
 def fa_to_hf(x: torch.Tensor, batch: int):
     """[batch * seqlen, heads, head_dim] -> [batch, heads, seqlen, head_dim] (moba/wrapper.py:18-26)."""
     return x.view(batch, -1, x.shape[1], x.shape[2]).permute(0, 2, 1, 3)
@@ -97,7 +104,14 @@ def moba_layer(
         # prefill phase: as the reference, `scaling` and the attention mask are not used here.
         # hf_to_fa is a view (no copy) when the tensors are transposed views of [batch, len, heads, dim] memory,
         # which is what the HuggingFace Llama attention passes (modeling_llama.py projects to [batch, len,
-        # heads * dim] and transposes), and for batch 1 in any layout.
+        # heads * dim] and transposes), and for batch 1 in any layout; any other layout is read in place per sequence.
+        if batch > 1 and getattr(moba_impl, "supports_grouped_kv", False) and not all(
+                _reshape_is_view(t) for t in (query, key, value)):
+            # [batch, heads, len, dim]-contiguous memory (a key/value cache): hf_to_fa would copy all three tensors.
+            # This package's implementation reads them in place, one call per sequence (moba_attn_batched).
+            from .moba_efficient import moba_attn_batched
+
+            return moba_attn_batched(query, key, value, moba_config.moba_chunk_size, moba_config.moba_topk), None
         query = hf_to_fa(query)
         key = hf_to_fa(key)
         value = hf_to_fa(value)

@@ -81,3 +81,42 @@ def test_llama_random_init_through_register_moba(cuda_device):
         ref = grads_d[name]
         assert torch.isfinite(g).all(), name
         assert (g - ref).abs().max() <= 5e-2 * max(float(ref.abs().max()), 1e-3) + 1e-4, name
+
+
+def test_batched_layout_is_read_in_place(cuda_device, monkeypatch):
+    """[batch, heads, len, dim]-contiguous tensors with batch > 1 (where the reference's hf_to_fa copies): the layer
+    hands the kernels views of the caller's memory, and the result and the gradients are bit for bit those of the
+    call on the copied [batch * len, heads, dim] tensors."""
+    from moba_b200 import MoBAConfig, check_kernel_status, moba_attn_varlen, moba_efficient, moba_layer
+    from moba_b200.wrapper import hf_to_fa
+
+    B, S, heads, kv_heads, chunk, topk = 3, 640, 4, 2, 128, 3
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    query = torch.randn(B, heads, S, 128, generator=g, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    key = torch.randn(B, kv_heads, S, 128, generator=g, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    value = torch.randn(B, kv_heads, S, 128, generator=g, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    d_out = torch.randn(B * S, heads, 128, generator=g, device=cuda_device).to(torch.bfloat16)
+
+    seen = []
+    real_forward = moba_efficient._forward
+
+    def spy(q, k, v, *a, **kw):
+        seen.append((q.untyped_storage().data_ptr(), k.untyped_storage().data_ptr(), v.untyped_storage().data_ptr()))
+        return real_forward(q, k, v, *a, **kw)
+
+    monkeypatch.setattr(moba_efficient, "_forward", spy)
+    out, _ = moba_layer(moba_attn_varlen, MoBAConfig(chunk, topk), _Causal(), query, key, value)
+    out.backward(d_out)
+    check_kernel_status(cuda_device)
+    want_ptrs = (query.untyped_storage().data_ptr(), key.untyped_storage().data_ptr(), value.untyped_storage().data_ptr())
+    assert len(seen) == B and all(p == want_ptrs for p in seen)          # the kernels saw the caller's memory
+    monkeypatch.setattr(moba_efficient, "_forward", real_forward)
+
+    q2, k2, v2 = (hf_to_fa(t.detach()).contiguous().requires_grad_() for t in (query, key, value))
+    cu = torch.tensor([i * S for i in range(B + 1)], dtype=torch.int32, device=cuda_device)
+    out2 = moba_attn_varlen(q2, k2, v2, cu, S, chunk, topk)
+    out2.backward(d_out)
+    check_kernel_status(cuda_device)
+    assert torch.equal(out, out2)
+    for got, ref in ((query.grad, q2.grad), (key.grad, k2.grad), (value.grad, v2.grad)):
+        assert torch.equal(hf_to_fa(got), ref)
