@@ -168,6 +168,9 @@ int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_
  *    part_lse [R*H] fp32
  * q/k/v: bf16 or f16. status: one int32 device word, zeroed by the caller; non-zero after the launch means
  * a bounded wait expired (see MOBA_ERR_DEVICE; read it with moba_check_status).
+ * softmax_scale (here and in the two backward tile entry points): the scale of the scores; <= 0 means 128^-0.5
+ * (moba/moba_efficient.py:86 uses head_dim^-0.5). Tensors of a head dim below 128 are passed zero-padded to 128
+ * columns with their own head_dim^-0.5: the padding changes no product.
  * parts (here and in the two backward tile entry points): 3 = both parts (the normal call), 1 = own-chunk part
  * only, 2 = list part only -- the two halves MixedAttention (moba/moba_efficient.py:67-267) runs as separate
  * flash calls; buffers of a part that is not requested may be NULL.
@@ -175,8 +178,8 @@ int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_
 int moba_attn_fwd(const void* q, const void* k, const void* v, int32_t dtype, int32_t H, int64_t stride_s,
                   int64_t stride_h, const moba_kv_layout* kv, const moba_plan_info* info, const int32_t* meta_dev,
                   const int32_t* list_off, const int32_t* work_off, const int32_t* list_tok, void* out,
-                  float* lse, void* part_o, float* part_lse, int32_t parts, int32_t* status, int32_t device,
-                  void* stream);
+                  float* lse, void* part_o, float* part_lse, int32_t parts, float softmax_scale, int32_t* status,
+                  int32_t device, void* stream);
 
 /*
  * Log-sum-exp merge of the self result with the <= kk gathered partial results of every (token, head),
@@ -213,7 +216,7 @@ int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* 
                        int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                        const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off, const void* qg, const void* dog,
                        const float* lse_g, const float* delta_g, const float* lse, const float* delta, void* dk,
-                       void* dv, int32_t parts, int32_t* status, int32_t device, void* stream);
+                       void* dv, int32_t parts, float softmax_scale, int32_t* status, int32_t device, void* stream);
 
 /*
  * Backward, query side, unrounded: dq of the self part -> dq_self [S,H,D] fp32; dq of every gathered row ->
@@ -226,7 +229,8 @@ int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_
                      const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off, const int32_t* work_off,
                      const int32_t* list_tok, const void* qg, const void* dog, const float* lse_g,
                      const float* delta_g, const float* lse, const float* delta, float* dq_self,
-                     float* part_dq, int32_t parts, int32_t* status, int32_t device, void* stream);
+                     float* part_dq, int32_t parts, float softmax_scale, int32_t* status, int32_t device,
+                     void* stream);
 
 /* dq[s,h,:] = round(dq_self[s,h,:] + sum_j part_dq[row_of[s,h,j], :]) (fp32 sum in slot order, one rounding
  * to `dtype`). Replaces the index_select backward (index_add) autograd runs for moba_q

@@ -56,6 +56,7 @@ class KvLayout(ctypes.Structure):
 _P = ctypes.c_void_p
 _I32 = ctypes.c_int32
 _I64 = ctypes.c_int64
+_F32 = ctypes.c_float
 _INFO = ctypes.POINTER(PlanInfo)
 _KV = ctypes.POINTER(KvLayout)      # None passes NULL: K / V laid out like q
 
@@ -72,15 +73,15 @@ SIGNATURES = {
     "moba_gate_topk": (ctypes.c_int, [_P, _I32, _I32, _I64, _I64, _P, _I32, _INFO, _P, _P, _P, _P, _P, _I32, _P]),
     "moba_build_lists": (ctypes.c_int, [_I32, _INFO, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _P]),
     "moba_attn_fwd": (ctypes.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P,
-                                     _P, _I32, _P, _I32, _P]),
+                                     _P, _I32, _F32, _P, _I32, _P]),
     "moba_merge_fwd": (ctypes.c_int, [_P, _P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),
     "moba_bwd_delta": (ctypes.c_int, [_P, _P, _I32, _I32, _I64, _P, _I32, _P]),
     "moba_gather_rows": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _INFO, _P, _P, _P, _P, _P, _P, _P,
                                         _I32, _P]),
     "moba_attn_bwd_dkdv": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P,
-                                          _P, _P, _P, _P, _I32, _P, _I32, _P]),
+                                          _P, _P, _P, _P, _I32, _F32, _P, _I32, _P]),
     "moba_attn_bwd_dq": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P,
-                                        _P, _P, _P, _P, _P, _P, _I32, _P, _I32, _P]),
+                                        _P, _P, _P, _P, _P, _P, _I32, _F32, _P, _I32, _P]),
     "moba_memcpy_2d": (ctypes.c_int, [_P, _I64, _P, _I64, _I64, _I64, _I32, _I32, _P]),
     "moba_merge_dq": (ctypes.c_int, [_P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),
     "moba_decode_ws_floats": (_I64, [_I32, _I32, _I32, _I32, _I32]),

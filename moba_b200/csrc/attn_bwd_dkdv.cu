@@ -183,8 +183,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         }
       }
       constexpr float kInvOne = kBf16 ? 1.0f : 1.0f / 256.0f;      // the ones tile holds 1 (bf16) or 256 (f16)
-      const uint32_t xl_a = ok_a ? split16<kBf16>(l_a * (-kInvOne / kSoftmaxScale)) : kMaskedPair<kBf16>;
-      const uint32_t xl_b = ok_b ? split16<kBf16>(l_b * (-kInvOne / kSoftmaxScale)) : kMaskedPair<kBf16>;
+      const uint32_t xl_a = ok_a ? split16<kBf16>(l_a * (-kInvOne / a.scale)) : kMaskedPair<kBf16>;
+      const uint32_t xl_b = ok_b ? split16<kBf16>(l_b * (-kInvOne / a.scale)) : kMaskedPair<kBf16>;
       const uint32_t xd_a = split16<kBf16>(-kInvOne * d_a), xd_b = split16<kBf16>(-kInvOne * d_b);
       int go = 1;
       if (g >= kStages) {
@@ -311,7 +311,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const int row = tid & 127, ci = warp >> 2;     // key row; which 32 of the 64 query columns of a half tile
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t pair_bar = 1 + (warp & 3);      // named barrier shared by warps w and w + 4 (same rows)
-    const float sc = kSoftmaxScale * kLog2e;
+    const float sc = a.scale * kLog2e, scale = a.scale;
     bool ok = true;
     int seg = 0;
     for (int g = 0; g < n_half; ++g) {
@@ -348,10 +348,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             if (row > col + 2) p2 = 0.f;
             if (row > col + 3) p3 = 0.f;
           }
-          const float e0 = p0 * (__uint_as_float(rd[4 * c]) * kSoftmaxScale);
-          const float e1 = p1 * (__uint_as_float(rd[4 * c + 1]) * kSoftmaxScale);
-          const float e2 = p2 * (__uint_as_float(rd[4 * c + 2]) * kSoftmaxScale);
-          const float e3 = p3 * (__uint_as_float(rd[4 * c + 3]) * kSoftmaxScale);
+          const float e0 = p0 * (__uint_as_float(rd[4 * c]) * scale);
+          const float e1 = p1 * (__uint_as_float(rd[4 * c + 1]) * scale);
+          const float e2 = p2 * (__uint_as_float(rd[4 * c + 2]) * scale);
+          const float e3 = p3 * (__uint_as_float(rd[4 * c + 3]) * scale);
           pp[2 * c] = pack2<kBf16>(p0, p1);
           pp[2 * c + 1] = pack2<kBf16>(p2, p3);
           pd[2 * c] = pack2<kBf16>(e0, e1);
@@ -399,7 +399,8 @@ extern "C" int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, c
                                   const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
                                   const void* qg, const void* dog,
                                   const float* lse_g, const float* delta_g, const float* lse, const float* delta,
-                                  void* dk, void* dv, int32_t parts, int32_t* status, int32_t device, void* stream) {
+                                  void* dk, void* dv, int32_t parts, float softmax_scale, int32_t* status,
+                                  int32_t device, void* stream) {
   using namespace moba;
   MOBA_REQUIRE(parts >= 1 && parts <= 3, MOBA_ERR_ARG, "parts=%d must be 1 (own chunk), 2 (lists) or 3 (both)", parts);
   int rc = check_bwd_args(q, k, v, d_out, dtype, H, stride_s, stride_h, info, meta_dev, lse, delta, status);
@@ -443,6 +444,7 @@ extern "C" int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, c
   a.status = status;
   a.n_experts = info->n_chunks * H;
   a.parts = parts;
+  a.scale = softmax_scale_or_default(softmax_scale);
   const size_t smem = sizeof(DkdvSmem) + 1024;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(info->n_qtiles, H / a.kv_rep);

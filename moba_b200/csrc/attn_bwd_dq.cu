@@ -152,11 +152,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     // list tiles read the list-ordered copies (one coalesced load per warp), own-chunk tiles the [S,H] arrays
     if constexpr (kGathered) {
       lse2 = a.lse_g[first + row] * kLog2e;
-      dlt = a.delta_g[first + row] * kSoftmaxScale;
+      dlt = a.delta_g[first + row] * a.scale;
     } else {
       const size_t i = static_cast<size_t>(first + row) * a.H + head;
       lse2 = a.lse[i] * kLog2e;
-      dlt = a.delta[i] * kSoftmaxScale;
+      dlt = a.delta[i] * a.scale;
     }
   }
 
@@ -265,7 +265,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     // ================= compute warps: thread = query row, 32 key columns =================
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t quad_bar = 1 + (warp & 3);      // named barrier shared by the four warps of a lane quarter
-    const float sc = kSoftmaxScale * kLog2e;
+    const float sc = a.scale * kLog2e, scale = a.scale;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       const int b = j & 1;
@@ -295,8 +295,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         for (int c = 0; c < 16; ++c) {
           const float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
           const float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
-          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), kSoftmaxScale, -dlt),
-                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), kSoftmaxScale, -dlt));
+          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
+                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
         }
       } else {
 #pragma unroll
@@ -306,8 +306,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
           if (c0 >= ncol) p0 = 0.f;
           if (c0 + 1 >= ncol) p1 = 0.f;
-          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), kSoftmaxScale, -dlt),
-                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), kSoftmaxScale, -dlt));
+          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
+                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
         }
       }
       // the 16-bit results land on TMEM columns [0, 64) of the S buffer, which other warps of the lane quarter
@@ -364,7 +364,8 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
                                 const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
                                 const int32_t* work_off, const int32_t* list_tok, const void* qg, const void* dog, const float* lse_g,
                                 const float* delta_g, const float* lse, const float* delta, float* dq,
-                                float* part_dq, int32_t parts, int32_t* status, int32_t device, void* stream) {
+                                float* part_dq, int32_t parts, float softmax_scale, int32_t* status, int32_t device,
+                                void* stream) {
   using namespace moba;
   MOBA_REQUIRE(parts >= 1 && parts <= 3, MOBA_ERR_ARG, "parts=%d must be 1 (own chunk), 2 (lists) or 3 (both)", parts);
   int rc = check_bwd_args(q, k, v, d_out, dtype, H, stride_s, stride_h, info, meta_dev, lse, delta, status);
@@ -398,6 +399,7 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
   a.q = static_cast<const uint16_t*>(q);
   a.d_out = static_cast<const uint16_t*>(d_out);
   a.stride_s = stride_s; a.stride_h = stride_h; a.H = H; a.lse_g = lse_g; a.delta_g = delta_g; a.parts = parts;
+  a.scale = softmax_scale_or_default(softmax_scale);
   a.plan = make_plan_dev(info, meta_dev);
   a.list_off = list_off; a.work_off = work_off; a.list_tok = list_tok;
   a.lse = lse; a.delta = delta;

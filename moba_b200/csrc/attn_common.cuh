@@ -7,7 +7,10 @@ namespace moba {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kSoftmaxScale = 0.08838834764831845f;   // 128^-0.5 (MoonshotAI/MoBA moba/moba_efficient.py:86)
+constexpr float kSoftmaxScale = 0.08838834764831845f;   // 128^-0.5 (MoonshotAI/MoBA moba/moba_efficient.py:86), the default
+// The scale the caller asked for: a value <= 0 means the default. Tensors of a smaller head dim reach the kernels
+// zero-padded to 128 columns (the products are unchanged) with their own head_dim^-0.5.
+inline float softmax_scale_or_default(float s) { return s > 0.f ? s : kSoftmaxScale; }
 
 struct BwdArgs {
   const uint16_t* q;
@@ -29,6 +32,7 @@ struct BwdArgs {
   int n_experts;
   int parts;             // bit 0: own-chunk (causal) tiles, bit 1: list tiles
   int kv_rep;            // query heads per key/value head (1 without grouped-query K / V)
+  float scale;           // softmax scale (head_dim^-0.5 of the caller's head dim)
 };
 
 // `nthreads` (a multiple of 16, at most 128) threads copy 128 rows x 256 B (row i from token row_tok[i], head

@@ -433,8 +433,8 @@ extern "C" int moba_attn_fwd(const void* q, const void* k, const void* v, int32_
                              int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                              const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
                              const int32_t* work_off, const int32_t* list_tok, void* out, float* lse,
-                             void* part_o, float* part_lse, int32_t parts, int32_t* status, int32_t device,
-                             void* stream) {
+                             void* part_o, float* part_lse, int32_t parts, float softmax_scale, int32_t* status,
+                             int32_t device, void* stream) {
   using namespace moba;
   int rc = check_common(q, H, stride_s, stride_h, info, meta_dev);
   if (rc) return rc;
@@ -462,7 +462,7 @@ extern "C" int moba_attn_fwd(const void* q, const void* k, const void* v, int32_
   a.lse = lse;
   a.status = status;
   a.n_experts = info->n_chunks * H;
-  a.scale_log2 = kSoftmaxScale * kLog2e;
+  a.scale_log2 = softmax_scale_or_default(softmax_scale) * kLog2e;
   FwdArgs g = a;
   g.out = static_cast<uint16_t*>(part_o);
   g.lse = part_lse;

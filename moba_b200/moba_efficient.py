@@ -56,7 +56,7 @@ def calc_chunks(cu_seqlen, moba_chunk_size):
 class _Context:
     """What forward keeps for backward: the plan, the query lists and the merged softmax statistics."""
 
-    __slots__ = ("plan", "lists", "row_of", "lse", "gate_dtype")
+    __slots__ = ("plan", "lists", "row_of", "lse", "gate_dtype", "scale")
 
 
 def _compute_dtype(t):
@@ -78,9 +78,10 @@ def _share_strides(q, k, v):
     return q.contiguous(), k.contiguous(), v.contiguous()
 
 
-def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, out=None):
+def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, out=None, scale=0.0):
     """Runs pool -> gate/top-k -> lists -> attention tiles -> merge. Returns (out in q.dtype, context). `out`:
-    optional contiguous [S, H, D] buffer of the compute dtype that receives the result."""
+    optional contiguous [S, H, D] buffer of the compute dtype that receives the result; `scale`: softmax scale
+    (0 = 128^-0.5; tensors of a smaller head dim arrive zero-padded to 128 columns with their own head_dim^-0.5)."""
     if k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2] or k.shape[1] < 1 \
             or q.shape[1] % k.shape[1] != 0:
         raise ValueError("k and v must have the shape of q, or the same shape with a head count that divides "
@@ -112,10 +113,10 @@ def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, out=None):
         longest = max((b - a for a, b in zip(plan.cu_host, plan.cu_host[1:])), default=1)
         plan = ops.Plan(plan.cu_host, max(longest, 1), 1, dev)
     qc, kc, vc = _share_strides(_as_compute(q), _as_compute(k), _as_compute(v))
-    out, lse, part_o, part_lse = ops.attn_fwd(qc, kc, vc, plan, lists, status, out=out)
+    out, lse, part_o, part_lse = ops.attn_fwd(qc, kc, vc, plan, lists, status, out=out, scale=scale)
     if plan.kk > 0:
         ops.merge_fwd(out, lse, plan, part_o, part_lse, row_of)
-    ctx.plan, ctx.lists, ctx.row_of, ctx.lse = plan, lists, row_of, lse
+    ctx.plan, ctx.lists, ctx.row_of, ctx.lse, ctx.scale = plan, lists, row_of, lse, scale
     return out, (qc, kc, vc), ctx
 
 
@@ -134,8 +135,9 @@ def _backward(qc, kc, vc, out, d_out, ctx, grads_out=None):
     # the rows every (chunk, head) list names, copied into list order once for both backward kernels
     gathered = ops.gather_rows(qc, d_out, plan, ctx.lists, ctx.lse, delta) if plan.kk > 0 else (None,) * 4
     dk, dv = ops.attn_bwd_dkdv(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered,
-                               out=grads_out[1:] if grads_out else None)
-    dq_self, part_dq = ops.attn_bwd_dq(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered)
+                               out=grads_out[1:] if grads_out else None, scale=ctx.scale)
+    dq_self, part_dq = ops.attn_bwd_dq(qc, kc, vc, d_out, plan, ctx.lists, ctx.lse, delta, status, gathered=gathered,
+                                       scale=ctx.scale)
     dq = ops.merge_dq(dq_self, plan, part_dq, ctx.row_of, qc.dtype, out=grads_out[0] if grads_out else None)
     return dq, dk, dv
 
@@ -145,16 +147,34 @@ class _MobaAttnFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, moba_chunk_size, moba_topk):
-        out, (qc, kc, vc), c = _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk)
+        D = q.shape[2]
+        if D > ops._lib.HEAD_DIM or D % 8 != 0 or D < 8:
+            raise ValueError(f"head_dim {D} is not supported: the kernels take a multiple of 8 up to {ops._lib.HEAD_DIM}")
+        scale = 0.0
+        if D < ops._lib.HEAD_DIM:
+            # the tiles are 128 columns wide: zero columns change neither q . k nor the pooled keys' scores, and the
+            # extra columns of v only produce zero columns of the result; the scale stays that of the real head dim
+            pad = (0, ops._lib.HEAD_DIM - D)
+            q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+            scale = D ** -0.5
+        out, (qc, kc, vc), c = _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, scale=scale)
         ctx.save_for_backward(qc, kc, vc, out)
         ctx.moba = c
         ctx.in_dtype = q.dtype
+        ctx.head_dim = D
+        if D < ops._lib.HEAD_DIM:
+            out = out[:, :, :D].contiguous()
         return out if out.dtype == q.dtype else out.to(q.dtype)
 
     @staticmethod
     def backward(ctx, d_out):
         qc, kc, vc, out = ctx.saved_tensors
+        D = ctx.head_dim
+        if D < ops._lib.HEAD_DIM:
+            d_out = torch.nn.functional.pad(d_out, (0, ops._lib.HEAD_DIM - D))
         dq, dk, dv = _backward(qc, kc, vc, out, d_out, ctx.moba)
+        if D < ops._lib.HEAD_DIM:
+            dq, dk, dv = (g[:, :, :D].contiguous() for g in (dq, dk, dv))
         if ctx.in_dtype != dq.dtype:
             dq, dk, dv = dq.to(ctx.in_dtype), dk.to(ctx.in_dtype), dv.to(ctx.in_dtype)
         return dq, dk, dv, None, None, None
@@ -346,8 +366,9 @@ def moba_attn_varlen(
     """MoBA attention over packed variable-length sequences (signature of moba/moba_efficient.py:270-278).
 
     Args:
-        q, k, v: [seqlen, head, head_dim] CUDA tensors, head_dim == 128, bf16 / fp16 (fp32 is accepted: the
-            gate runs on the fp32 values, the attention tiles on a bf16 copy). Beyond the reference, k and v may
+        q, k, v: [seqlen, head, head_dim] CUDA tensors, bf16 / fp16 (fp32 is accepted: the gate runs on the fp32
+            values, the attention tiles on a bf16 copy). head_dim 128 is the native tile width; a smaller head_dim
+            (a multiple of 8) runs on zero-padded copies with its own head_dim^-0.5, so 64 costs what 128 does. Beyond the reference, k and v may
             carry fewer heads than q (grouped-query attention, at most 16 query heads per key/value head): query
             head h then reads key/value head h // (heads of q // heads of k), the result equals the call with
             k.repeat_interleave(...) / v.repeat_interleave(...) (what moba/wrapper.py:59-61 feeds the reference),

@@ -262,7 +262,7 @@ def build_lists(plan, H, sel, tile_cnt, status=None):
     return list_off, work_off, list_tok, row_of
 
 
-def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None):
+def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None, scale=0.0):
     """Self-chunk causal attention -> (out, lse); gathered rows -> (part_o, part_lse).
 
     parts: 3 both, 1 own-chunk part only, 2 list part only (buffers of the other part are left unwritten).
@@ -283,7 +283,7 @@ def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None):
     with _timed("attn_fwd", q.device):
         call("moba_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _DTYPES[q.dtype], H, q.stride(0), q.stride(1), kv,
              ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(out),
-             _ptr(lse), _ptr(part_o), _ptr(part_lse), parts, _ptr(status), _dev_index(q), _stream(q.device))
+             _ptr(lse), _ptr(part_o), _ptr(part_lse), parts, float(scale), _ptr(status), _dev_index(q), _stream(q.device))
     return out, lse, part_o, part_lse
 
 
@@ -320,7 +320,7 @@ def gather_rows(q, d_out, plan, lists, lse, delta):
     return qg, dog, lse_g, delta_g
 
 
-def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, out=None):
+def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, out=None, scale=0.0):
     """dk, dv [S_k, H_kv, D] (summed over the query heads that share a key/value head). `gathered` = (qg, dog,
     lse_g, delta_g) when the caller already holds the rows in list order (else they are produced here by
     gather_rows)."""
@@ -338,12 +338,12 @@ def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gath
     with _timed("attn_bwd_dkdv", q.device):
         call("moba_attn_bwd_dkdv", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0),
              q.stride(1), kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(qg), _ptr(dog), _ptr(lse_g),
-             _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dk), _ptr(dv), parts, _ptr(status), _dev_index(q),
+             _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dk), _ptr(dv), parts, float(scale), _ptr(status), _dev_index(q),
              _stream(q.device))
     return dk, dv
 
 
-def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None):
+def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, scale=0.0):
     """Unrounded dq pieces: (dq_self [S,H,D] fp32, part_dq [R*H, D] fp32). `gathered` = (qg, dog, lse_g, delta_g),
     the rows in list order (gather_rows); produced here when not given."""
     S, H, D = q.shape
@@ -358,7 +358,7 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
         call("moba_attn_bwd_dq", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0),
              q.stride(1), kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok),
              _ptr(qg), _ptr(dog), _ptr(lse_g), _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dq_self), _ptr(part_dq),
-             parts, _ptr(status), _dev_index(q), _stream(q.device))
+             parts, float(scale), _ptr(status), _dev_index(q), _stream(q.device))
     return dq_self, part_dq
 
 

@@ -51,18 +51,22 @@ def _decode_attention(query, key, value, scaling):
     flash_attn_func(..., causal=True) call (moba/wrapper.py:76-82); returns [batch, q_len, heads, dim].
 
     16-bit CUDA tensors with head_dim 128 that need no gradient run the library's decode kernel
-    (moba_decode_attn: K / V streamed once, grouped-query heads sharing the tiles). Anything else -- other head
-    dims, fp32, CPU tensors, a call under autograd -- is outside what the kernels cover and goes through torch's
-    scaled-dot-product attention."""
+    (moba_decode_attn: K / V streamed once, grouped-query heads sharing the tiles); with gradients (and the default
+    scale) the attention tile kernels run it as two merged parts (_decode_attention_autograd). Anything else --
+    other head dims, fp32, CPU tensors, a caller-chosen scale under autograd -- is outside what the kernels cover
+    and goes through torch's scaled-dot-product attention."""
     b, hq, lq, d = query.shape
     hkv, lk = key.shape[1], key.shape[2]
     needs_grad = torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad)
-    if (query.is_cuda and d == 128 and lk >= lq and query.dtype in (torch.bfloat16, torch.float16)
-            and key.dtype == query.dtype and value.dtype == query.dtype and not needs_grad):
+    kernel_ok = (query.is_cuda and d == 128 and lk >= lq and query.dtype in (torch.bfloat16, torch.float16)
+                 and key.dtype == query.dtype and value.dtype == query.dtype)
+    if kernel_ok and not needs_grad:
         from . import ops
         from .moba_efficient import _status_word
 
         return ops.decode_attn(query, key, value, scaling, status=_status_word(query.device))
+    if kernel_ok and hq % hkv == 0 and (scaling is None or abs(float(scaling) - d ** -0.5) < 1e-7):
+        return _decode_attention_autograd(query, key, value)
     if lk < lq:
         raise ValueError(f"decode needs kv_len >= q_len (got q_len {lq}, kv_len {lk}): the causal mask is aligned to "
                          "the end of the keys, so earlier query positions would see no key at all")
@@ -72,6 +76,47 @@ def _decode_attention(query, key, value, scaling):
     out = torch.nn.functional.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling,
                                                            enable_gqa=hkv != hq)
     return out.transpose(1, 2)
+
+
+def _decode_attention_autograd(query, key, value):
+    """The decode step with gradients, on the attention tile kernels (no library attention): bottom-right aligned
+    causal attention of q_len positions over kv_len keys is the two-part attention MixedAttention computes --
+    part 1, causal attention of the queries over the last q_len keys; part 2, full attention of the same queries over
+    the kv_len - q_len keys before them, one (batch, query head) pair per key/value segment -- merged by their
+    log-sum-exps. The operands are cut and regrouped with differentiable torch ops, so the gradients reach query,
+    key and value through autograd. Returns [batch, q_len, q_heads, dim] like the inference kernel."""
+    from .moba_efficient import MixedAttention
+
+    b, hq, lq, d = query.shape
+    hkv, lk = key.shape[1], key.shape[2]
+    rep, dev = hq // hkv, query.device
+    q1 = query.permute(0, 2, 1, 3).reshape(b * lq, hq, d)                                   # tokens (batch, l)
+    k_tail = key[:, :, lk - lq:].repeat_interleave(rep, dim=1) if rep > 1 else key[:, :, lk - lq:]
+    v_tail = value[:, :, lk - lq:].repeat_interleave(rep, dim=1) if rep > 1 else value[:, :, lk - lq:]
+    k1 = k_tail.permute(0, 2, 1, 3).reshape(b * lq, hq, d)
+    v1 = v_tail.permute(0, 2, 1, 3).reshape(b * lq, hq, d)
+    cu_self = torch.arange(b + 1, device=dev, dtype=torch.int32) * lq
+    n_pre = lk - lq
+    e = b * hq                                                                              # (batch, head) segments
+    if n_pre > 0:
+        moba_q = query.reshape(e * lq, 1, d)                                                # rows (batch, head, l)
+        k_pre = key[:, :, :n_pre].repeat_interleave(rep, dim=1) if rep > 1 else key[:, :, :n_pre]
+        v_pre = value[:, :, :n_pre].repeat_interleave(rep, dim=1) if rep > 1 else value[:, :, :n_pre]
+        moba_kv = torch.stack((k_pre.reshape(e * n_pre, 1, d), v_pre.reshape(e * n_pre, 1, d)), dim=1)
+        cu_q = torch.arange(e + 1, device=dev, dtype=torch.int32) * lq
+        cu_kv = torch.arange(e + 1, device=dev, dtype=torch.int32) * n_pre
+        bi = torch.arange(b, device=dev).view(b, 1, 1)
+        hi = torch.arange(hq, device=dev).view(1, hq, 1)
+        li = torch.arange(lq, device=dev).view(1, 1, lq)
+        sh = ((bi * lq + li) * hq + hi).reshape(-1)                                         # target (token, head) row
+    else:
+        moba_q = query.new_zeros((0, 1, d))
+        moba_kv = query.new_zeros((0, 2, 1, d))
+        cu_q = cu_kv = torch.zeros(1, device=dev, dtype=torch.int32)
+        sh = torch.zeros(0, device=dev, dtype=torch.int64)
+    out = MixedAttention.apply(q1.contiguous(), k1.contiguous(), v1.contiguous(), cu_self, moba_q.contiguous(),
+                               moba_kv, cu_q, cu_kv, lq, max(n_pre, 1), sh)
+    return out.view(b, lq, hq, d)
 
 
 def moba_layer(
@@ -105,7 +150,7 @@ def moba_layer(
         # hf_to_fa is a view (no copy) when the tensors are transposed views of [batch, len, heads, dim] memory,
         # which is what the HuggingFace Llama attention passes (modeling_llama.py projects to [batch, len,
         # heads * dim] and transposes), and for batch 1 in any layout; any other layout is read in place per sequence.
-        if batch > 1 and getattr(moba_impl, "supports_grouped_kv", False) and not all(
+        if batch > 1 and head_dim == 128 and getattr(moba_impl, "supports_grouped_kv", False) and not all(
                 _reshape_is_view(t) for t in (query, key, value)):
             # [batch, heads, len, dim]-contiguous memory (a key/value cache): hf_to_fa would copy all three tensors.
             # This package's implementation reads them in place, one call per sequence (moba_attn_batched).

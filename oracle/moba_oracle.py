@@ -18,8 +18,9 @@ What is restated (numpy, fp32 arithmetic, file:line in MoonshotAI/MoBA):
                        dependency that is not part of the reference checkout, so its published definition is
                        restated -- softmax(scale * q k^T) v with the causal mask aligned to the bottom-right corner
                        (query i of q_len sees keys 0 .. kv_len - q_len + i), grouped-query heads sharing key/value
-                       head h // (q_heads // kv_heads). Parity unpinned for this one function: the reference holds
-                       no test or fixture for its decode branch and flash-attn's private API is not runnable here.
+                       head h // (q_heads // kv_heads). The reference holds no test or fixture for its decode branch; this
+                       function is pinned instead against flash_attn_func itself, run on the GPU from the installed
+                       flash-attn package (tests/test_gpu_decode.py), and is unpinned where that cannot run.
 
 Parity pin: tests/test_oracle_golden.py checks every function here against fixtures produced by running
 the reference's own moba_attn_varlen_naive (tests/golden/make_golden.py is the generating script).

@@ -122,3 +122,35 @@ def test_decode_oracle_and_kernel_against_flash_attn_func(cuda_device, B, Hq, Hk
     assert np.abs(want - ref).max() < 1e-2 and np.abs(want - ref).mean() < 5e-4      # the oracle restates that call
     got = t2n(ops.decode_attn(tq, tk, tv, scale))
     H.assert_parity("kernel vs flash_attn_func", got, ref)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk", [(2, 4, 2, 3, 517), (1, 8, 1, 1, 1000), (1, 2, 2, 7, 7), (1, 4, 4, 130, 400)])
+def test_decode_branch_under_autograd_runs_on_the_kernels(cuda_device, monkeypatch, B, Hq, Hkv, Lq, Lk):
+    """q_len != kv_len with gradients (moba/wrapper.py:76-82 is differentiable through flash_attn_func): the layer
+    runs the attention tile kernels as two merged parts, no library attention; out and the gradients of query, key
+    and value against an fp64 evaluation of bottom-right aligned causal attention."""
+    from moba_b200 import MoBAConfig, check_kernel_status, moba_layer
+
+    (q, k, v), (tq, tk, tv) = _inputs(11, B, Hq, Hkv, Lq, Lk, "bf16", cuda_device)
+    tq, tk, tv = (t.requires_grad_() for t in (tq, tk, tv))
+
+    def no_sdpa(*a, **kw):
+        raise AssertionError("the decode branch fell back to torch's attention")
+
+    monkeypatch.setattr(torch.nn.functional, "scaled_dot_product_attention", no_sdpa)
+    out, _ = moba_layer(None, MoBAConfig(64, 3), _Causal(), tq, tk, tv, scaling=128 ** -0.5)
+    g = torch.Generator(device=cuda_device).manual_seed(3)
+    d_out = torch.randn(out.shape, generator=g, device=cuda_device).to(torch.bfloat16)
+    out.backward(d_out)
+    check_kernel_status(cuda_device)
+    assert out.shape == (B, Lq, Hq, 128)
+
+    rq, rk, rv = (t.detach().double().requires_grad_() for t in (tq, tk, tv))
+    rep = Hq // Hkv
+    s = torch.einsum("bhqd,bhkd->bhqk", rq, rk.repeat_interleave(rep, 1)) * 128 ** -0.5
+    mask = torch.arange(Lk, device=cuda_device)[None, :] <= (torch.arange(Lq, device=cuda_device)[:, None] + (Lk - Lq))
+    ref = torch.einsum("bhqk,bhkd->bqhd", s.masked_fill(~mask, float("-inf")).softmax(-1), rv.repeat_interleave(rep, 1))
+    ref.backward(d_out.double())
+    H.assert_parity("out", t2n(out), ref.detach().float().cpu().numpy())
+    for name, got, want in (("dq", tq.grad, rq.grad), ("dk", tk.grad, rk.grad), ("dv", tv.grad, rv.grad)):
+        H.assert_parity(name, t2n(got) / rep ** 0.5, want.float().cpu().numpy() / rep ** 0.5)

@@ -310,3 +310,25 @@ def test_gate_tensor_pipe_matches_fma(cuda_device, dtype, S, cu, chunk):
         assert (sc.max() - sc.min()).item() <= 1e-3 * sc.abs().max().item(), (s_i, h_i, only, sc.tolist())
     if bool(same.all()):
         assert torch.equal(cnt_a, cnt_b)
+
+
+@pytest.mark.parametrize("head_dim", [64, 96, 32])
+def test_smaller_head_dims(cuda_device, head_dim):
+    """head_dim below the 128-column tile width: the call pads with zero columns and keeps head_dim^-0.5
+    (moba/moba_efficient.py:86), so the result is that of the reference at that head dim."""
+    rng = np.random.RandomState(head_dim)
+    S, heads, chunk, topk = 1100, 2, 128, 3
+    cu = [0, 500, 1100]
+    q, k, v, d_out = (orc.round_bf16(rng.randn(S, heads, head_dim).astype(np.float32)) for _ in range(4))
+    got = check_against_oracle(q, k, v, d_out, cu, chunk, topk, cuda_device, tag=f"D{head_dim}:")
+    assert got[0].shape == (S, heads, head_dim) and got[3].shape == (S, heads, head_dim)
+
+
+def test_unsupported_head_dims_are_refused(cuda_device):
+    from moba_b200 import moba_attn_varlen
+
+    cu = torch.tensor([0, 256], dtype=torch.int32, device=cuda_device)
+    for d in (256, 100):
+        x = torch.zeros(256, 1, d, dtype=torch.bfloat16, device=cuda_device)
+        with pytest.raises(ValueError, match="head_dim"):
+            moba_attn_varlen(x, x, x, cu, 256, 64, 2)
