@@ -293,6 +293,12 @@ int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_rows, const
                               const void* b, float* c, int32_t dtype, int32_t* status, int32_t device,
                               void* stream);
 
+/* CTA-pair self test (no counterpart in the reference): S = Q K^T for q [256,128] and k [128,128], O = (S / 16
+ * rounded to 16 bit) V for v [128,128], computed by two CTAs of one cluster with 256-row tcgen05 instructions
+ * (cta_group::2): s_out, o_out [256,128] fp32. Used by the tests to pin the operand split between the two CTAs. */
+int moba_selftest_umma_pair(const void* q, const void* k, const void* v, float* s_out, float* o_out, int32_t dtype,
+                            int32_t* status, int32_t device, void* stream);
+
 /*
  * Failure-path self test (not on any product path): n_ctas CTAs allocate tensor memory and wait on an mbarrier that
  * nothing arrives on, for at most limit_ns nanoseconds (1e3 .. 1e8). The waits run out, the kernel sets *status to

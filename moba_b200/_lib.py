@@ -90,6 +90,7 @@ SIGNATURES = {
     "moba_check_status": (ctypes.c_int, [_P, _I32, _P]),
     "moba_selftest_umma": (ctypes.c_int, [_I32, _P, _P, _P, _I32, _P, _I32, _P]),
     "moba_selftest_umma_gather": (ctypes.c_int, [_I32, _P, _I32, _P, _P, _P, _I32, _P, _I32, _P]),
+    "moba_selftest_umma_pair": (ctypes.c_int, [_P, _P, _P, _P, _P, _I32, _P, _I32, _P]),
     "moba_selftest_wait_timeout": (ctypes.c_int, [_I64, _I32, _P, _I32, _P]),
 }
 

@@ -204,6 +204,163 @@ extern "C" int moba_selftest_umma_gather(int32_t mode, const void* a, int32_t a_
 }
 
 // ---------------------------------------------------------------------------------------------------
+// CTA-pair self test: two CTAs of one cluster compute S = Q K^T for 256 query rows x 128 keys with one
+// 256-row MMA per k-step (operands in shared memory, each CTA holding its 128 rows of Q and 64 of the 128 keys),
+// hand S / 16 back as 16-bit values in tensor memory and compute O = (S / 16) V with the A operand read from tensor
+// memory (each CTA holding 64 of V's 128 columns). Checks the operand split between the CTAs, the loads that
+// signal the even CTA's barrier from both CTAs, arrivals across the pair and the commit that reaches both.
+namespace moba {
+namespace {
+
+struct __align__(1024) PairSmem {
+  uint8_t q[2][16384];     // own 128 rows: [128 x 64] sub-tiles (d 0..63 | d 64..127), 128-byte swizzle
+  uint8_t k[2][8192];      // own 64 keys: [64 x 64] sub-tiles
+  uint8_t v[16384];        // 128 keys x own 64 columns
+  uint64_t bar_load, bar_s, bar_p, bar_o;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+selftest_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, float* __restrict__ s_out,
+                     float* __restrict__ o_out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  PairSmem& sm = *reinterpret_cast<PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();
+  WaitCtx wctx{&sm.abort_flag, status, 200000000ull};
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.bar_load, 1);
+    mbar_init(&sm.bar_s, 1);
+    mbar_init(&sm.bar_p, 256);          // every thread of both CTAs
+    mbar_init(&sm.bar_o, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(&sm.tmem_base, 256);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();                    // barriers of both CTAs exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t load_bar0 = cluster_map_shared(smem_u32(&sm.bar_load), 0);
+  const uint32_t p_bar0 = cluster_map_shared(smem_u32(&sm.bar_p), 0);
+
+  if (tid == 0) {
+    if (rank == 0) mbar_arrive_expect_tx(&sm.bar_load, 2u * (32768u + 16384u + 16384u));
+    tma_load_3d_pair(smem_u32(sm.q[0]), &map_q, load_bar0, 0, 0, static_cast<int>(rank) * 128);
+    tma_load_3d_pair(smem_u32(sm.q[1]), &map_q, load_bar0, 64, 0, static_cast<int>(rank) * 128);
+    tma_load_3d_pair(smem_u32(sm.k[0]), &map_k, load_bar0, 0, 0, static_cast<int>(rank) * 64);
+    tma_load_3d_pair(smem_u32(sm.k[1]), &map_k, load_bar0, 64, 0, static_cast<int>(rank) * 64);
+    tma_load_3d_pair(smem_u32(sm.v), &map_v, load_bar0, static_cast<int>(rank) * 64, 0, 0);
+  }
+  bool ok = true;
+  if (warp == 0 && rank == 0) {
+    const uint32_t leader = elect_one();
+    ok = __all_sync(0xffffffffu, mbar_wait_cluster(&sm.bar_load, 0, wctx));
+    if (ok) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = umma_idesc(256, 128, kBf16, false, false);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t qoff = ((ks >> 2) * 16384u + (ks & 3) * 32u) >> 4;
+        const uint32_t koff = ((ks >> 2) * 8192u + (ks & 3) * 32u) >> 4;
+        umma_ss_pair_w(leader, tmem, umma_smem_desc(smem_u32(sm.q[0]), 16, 1024) + qoff,
+                       umma_smem_desc(smem_u32(sm.k[0]), 16, 1024) + koff, idesc, ks > 0);
+      }
+      umma_commit_pair_w(leader, &sm.bar_s);
+    }
+  }
+  ok = mbar_wait(&sm.bar_s, 0, wctx);
+  tc_fence_after_sync();
+  if (ok) {
+    const size_t row = static_cast<size_t>(rank) * 128 + tid;
+    uint32_t pk[64];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t r[32];
+      tmem_ld32(lane_addr + i * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) s_out[row * 128 + i * 32 + j] = __uint_as_float(r[j]);
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        pk[i * 16 + j] = pack2<kBf16>(__uint_as_float(r[2 * j]) * 0.0625f, __uint_as_float(r[2 * j + 1]) * 0.0625f);
+    }
+    // every load of the row is complete (tmem_wait_ld) before the packed values go over its first 64 columns
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = pk[i * 32 + j];
+      tmem_st32(lane_addr + i * 32, r);
+    }
+    tmem_wait_st();
+    tc_fence_before_sync();
+    mbar_arrive_cluster(p_bar0);
+  }
+  if (warp == 0 && rank == 0) {
+    const uint32_t leader = elect_one();
+    ok = __all_sync(0xffffffffu, mbar_wait_cluster(&sm.bar_p, 0, wctx));
+    if (ok) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc = umma_idesc(256, 128, kBf16, false, true);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma_ts_pair_w(leader, tmem + 128, tmem + ks * 8, umma_smem_desc(smem_u32(sm.v), 16384, 1024) + ((ks * 2048u) >> 4),
+                       idesc, ks > 0);
+      umma_commit_pair_w(leader, &sm.bar_o);
+    }
+  }
+  ok = mbar_wait(&sm.bar_o, 0, wctx);
+  tc_fence_after_sync();
+  if (ok) {
+    const size_t row = static_cast<size_t>(rank) * 128 + tid;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t r[32];
+      tmem_ld32(lane_addr + 128 + i * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o_out[row * 128 + i * 32 + j] = __uint_as_float(r[j]);
+    }
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();                    // neither CTA leaves while the other may still signal or read it
+  if (warp == 0) tmem_dealloc_pair(tmem, 256);
+}
+
+}  // namespace
+}  // namespace moba
+
+extern "C" int moba_selftest_umma_pair(const void* q, const void* k, const void* v, float* s_out, float* o_out,
+                                       int32_t dtype, int32_t* status, int32_t device, void* stream) {
+  using namespace moba;
+  MOBA_REQUIRE(q && k && v && s_out && o_out && status, MOBA_ERR_ARG, "null pointer argument");
+  MOBA_REQUIRE(dtype == MOBA_DTYPE_BF16 || dtype == MOBA_DTYPE_F16, MOBA_ERR_ARG, "dtype must be bf16 or f16");
+  MOBA_SET_DEVICE(device);
+  CUtensorMap mq, mk, mv;
+  int rc = make_tensor_map_shd(&mq, q, dtype, 256, 1, 128, 128, 128);
+  if (rc) return rc;
+  rc = make_tensor_map_shd(&mk, k, dtype, 128, 1, 128, 128, 64);
+  if (rc) return rc;
+  rc = make_tensor_map_shd(&mv, v, dtype, 128, 1, 128, 128, 128);
+  if (rc) return rc;
+  const size_t smem = sizeof(PairSmem) + 1024;
+  auto kern = dtype == MOBA_DTYPE_BF16 ? selftest_pair_kernel<true> : selftest_pair_kernel<false>;
+  MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<2, 128, smem, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, s_out, o_out, status);
+  MOBA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------
 // Failure-path self test: a CTA allocates tensor memory and waits on an mbarrier that nothing arrives on, with
 // the wait limit given by the caller. The wait must run out, set the status word to 1 (kStatusWaitTimeout),
 // and the CTA must still release its tensor memory and return, leaving the context usable.

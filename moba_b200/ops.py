@@ -435,6 +435,18 @@ def selftest_umma(mode, a, b):
     return c
 
 
+def selftest_umma_pair(q, k, v):
+    """S = Q K^T and O = (S / 16, rounded to 16 bit) V for q [256,128], k, v [128,128], computed by a pair of CTAs
+    with 256-row instructions; returns fp32 (S, O), [256,128] each."""
+    s_out = torch.zeros((256, 128), dtype=torch.float32, device=q.device)
+    o_out = torch.zeros((256, 128), dtype=torch.float32, device=q.device)
+    status = new_status(q.device)
+    call("moba_selftest_umma_pair", _ptr(q), _ptr(k), _ptr(v), _ptr(s_out), _ptr(o_out), _DTYPES[q.dtype],
+         _ptr(status), _dev_index(q), _stream(q.device))
+    check_status(status)
+    return s_out, o_out
+
+
 def selftest_wait_timeout(status, limit_ns=1_000_000, n_ctas=4):
     """Launches CTAs that wait on a barrier nothing arrives on; the waits run out after limit_ns and set `status`
     (a zeroed device word) to 1. The kernel frees its tensor memory and returns."""

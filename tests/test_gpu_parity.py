@@ -58,6 +58,24 @@ def test_umma_selftest(cuda_device, mode, dtype):
     assert (c - ref).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_umma_pair_selftest(cuda_device, dtype):
+    """256-row instructions over a pair of CTAs: each CTA's half of the rows, of the keys (S) and of the value
+    columns (O) must land where a plain matrix product puts them."""
+    from moba_b200 import ops
+
+    torch.manual_seed(7)
+    q = torch.randn(256, 128, device=cuda_device).to(TORCH_DT[dtype])
+    k = torch.randn(128, 128, device=cuda_device).to(TORCH_DT[dtype])
+    v = torch.randn(128, 128, device=cuda_device).to(TORCH_DT[dtype])
+    s, o = ops.selftest_umma_pair(q, k, v)
+    s_ref = q.float() @ k.float().T
+    assert (s - s_ref).abs().max().item() < 1e-3
+    p = (s * 0.0625).to(TORCH_DT[dtype]).float()          # what the kernel hands to the second product
+    o_ref = p @ v.float()
+    assert (o - o_ref).abs().max().item() < 2e-3
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
 def test_pool_keys_bit_exact_on_fixture_shapes(cuda_device, dtype):
     from moba_b200 import ops
