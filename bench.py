@@ -39,6 +39,8 @@ CONFIGS = {
     31: dict(lens=[131072], heads=4, kv_heads=1, chunk=4096, topk=12, off_std=0.5, backward=True),
     # varlen training batch: 16 sequences, lengths 512 * randint(8, 128) from random.Random(0)
     4: dict(lens=None, heads=32, kv_heads=32, chunk=512, topk=3, off_std=0.0, backward=True),
+    # a 2-head slice of it, small enough for an ncu capture
+    41: dict(lens=None, heads=2, kv_heads=2, chunk=512, topk=3, off_std=0.0, backward=True),
     # 1M-token prefill, forward only (meant for 8 GPUs, 4 heads each); 51 = one GPU's share of it
     5: dict(lens=[1048576], heads=32, kv_heads=8, chunk=4096, topk=12, off_std=0.5, backward=False),
     51: dict(lens=[1048576], heads=4, kv_heads=1, chunk=4096, topk=12, off_std=0.5, backward=False),
@@ -57,6 +59,7 @@ def _varlen_lengths(seed=0, n=16):
 
 
 CONFIGS[4]["lens"] = _varlen_lengths()
+CONFIGS[41]["lens"] = _varlen_lengths()
 
 
 def selected_pairs(lens, chunk, topk):
