@@ -223,7 +223,12 @@ int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* 
  * part_dq [R*H, D] fp32. List tiles read their query-side rows from the list-ordered copies qg / dog / lse_g /
  * delta_g (moba_gather_rows; may be NULL when no list part is requested), own-chunk tiles from q / d_out / lse /
  * delta. Replaces the dq halves of moba/moba_efficient.py:208-264.
+ * parts: bit 0 = own-chunk tiles, bit 1 = list tiles. The kernel has two forms with bit-identical results -- one
+ * query tile per CTA, and a persistent CTA per SM that walks its share of the tiles -- chosen by chunk size (the
+ * persistent form up to 2048 keys); MOBA_DQ_FORM_TILE or MOBA_DQ_FORM_PERSISTENT or'ed into parts names one.
  */
+#define MOBA_DQ_FORM_TILE 0x10
+#define MOBA_DQ_FORM_PERSISTENT 0x20
 int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype,
                      int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                      const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off, const int32_t* work_off,

@@ -856,7 +856,10 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
                                 float* part_dq, int32_t parts, float softmax_scale, int32_t* status, int32_t device,
                                 void* stream) {
   using namespace moba;
+  const int32_t form = parts & (MOBA_DQ_FORM_TILE | MOBA_DQ_FORM_PERSISTENT);
+  parts &= ~(MOBA_DQ_FORM_TILE | MOBA_DQ_FORM_PERSISTENT);
   MOBA_REQUIRE(parts >= 1 && parts <= 3, MOBA_ERR_ARG, "parts=%d must be 1 (own chunk), 2 (lists) or 3 (both)", parts);
+  MOBA_REQUIRE(form != (MOBA_DQ_FORM_TILE | MOBA_DQ_FORM_PERSISTENT), MOBA_ERR_ARG, "two kernel forms named in parts");
   int rc = check_bwd_args(q, k, v, d_out, dtype, H, stride_s, stride_h, info, meta_dev, lse, delta, status);
   if (rc) return rc;
   MOBA_REQUIRE(dq || !(parts & 1), MOBA_ERR_ARG, "null pointer argument");
@@ -917,7 +920,7 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
   };
   // Query tiles with few key tiles go through the persistent kernel (the per-tile set-up is what they spend their
   // time on); long ones through the one-tile-per-CTA kernel, whose steady state is a few percent faster.
-  const bool persist = info->chunk_size <= 16 * MOBA_TILE;
+  const bool persist = form ? form == MOBA_DQ_FORM_PERSISTENT : info->chunk_size <= 16 * MOBA_TILE;
   if (persist) {
     int n_sm = 0;
     MOBA_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));

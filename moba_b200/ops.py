@@ -343,9 +343,14 @@ def attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gath
     return dk, dv
 
 
-def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, scale=0.0):
+_DQ_FORMS = {None: 0, "tile": 0x10, "persistent": 0x20}
+
+
+def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gathered=None, scale=0.0, form=None):
     """Unrounded dq pieces: (dq_self [S,H,D] fp32, part_dq [R*H, D] fp32). `gathered` = (qg, dog, lse_g, delta_g),
-    the rows in list order (gather_rows); produced here when not given."""
+    the rows in list order (gather_rows); produced here when not given. `form` names one of the kernel's two forms
+    ("tile": one query tile per CTA, "persistent": one CTA per SM walking its tiles; same bits either way) instead of
+    leaving the choice to the chunk size."""
     S, H, D = q.shape
     kv = _kv_layout(q, k, v)
     list_off, work_off, list_tok = lists
@@ -358,7 +363,7 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
         call("moba_attn_bwd_dq", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0),
              q.stride(1), kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok),
              _ptr(qg), _ptr(dog), _ptr(lse_g), _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dq_self), _ptr(part_dq),
-             parts, float(scale), _ptr(status), _dev_index(q), _stream(q.device))
+             parts | _DQ_FORMS[form], float(scale), _ptr(status), _dev_index(q), _stream(q.device))
     return dq_self, part_dq
 
 

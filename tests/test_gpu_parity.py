@@ -350,3 +350,37 @@ def test_unsupported_head_dims_are_refused(cuda_device):
         x = torch.zeros(256, 1, d, dtype=torch.bfloat16, device=cuda_device)
         with pytest.raises(ValueError, match="head_dim"):
             moba_attn_varlen(x, x, x, cu, 256, 64, 2)
+
+
+@pytest.mark.parametrize("chunk,topk", [(256, 3), (1024, 4), (4096, 3)])
+def test_dq_kernel_forms_give_the_same_bits(cuda_device, chunk, topk):
+    """The dQ kernel's two forms (one query tile per CTA; a persistent CTA per SM walking its tiles, several rounds
+    each here) run the same arithmetic in the same order: dq_self and part_dq are bit for bit the same, on a ragged
+    batch with partial tiles."""
+    from moba_b200 import ops
+
+    dev = cuda_device
+    lens = [5000, 37, 12288 + 77, 128, 20000]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    S, H = cu[-1], 3
+    g = torch.Generator(device=dev).manual_seed(11)
+    q, k, v, d_out = (torch.randn(S, H, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(4))
+    plan = ops.get_plan(cu, chunk, topk, dev)
+    status = ops.new_status(dev)
+    sel, _, tile_cnt = ops.gate_topk(q, ops.pool_keys(k, plan), plan, status=status)
+    list_off, work_off, list_tok, row_of = ops.build_lists(plan, H, sel, tile_cnt, status=status)
+    lists = (list_off, work_off, list_tok)
+    out, lse, part_o, part_lse = ops.attn_fwd(q, k, v, plan, lists, status)
+    ops.merge_fwd(out, lse, plan, part_o, part_lse, row_of)
+    delta = ops.bwd_delta(out, d_out)
+    gathered = ops.gather_rows(q, d_out, plan, lists, lse, delta)
+    got = {}
+    for form in ("tile", "persistent"):
+        dq_self, part_dq = ops.attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, gathered=gathered, form=form)
+        got[form] = (dq_self, part_dq[: plan.rows_total(H)])
+    ops.check_status(status)
+    assert torch.equal(got["tile"][0], got["persistent"][0])
+    assert torch.equal(got["tile"][1], got["persistent"][1])
+    assert got["tile"][0].abs().max().item() > 0
