@@ -332,7 +332,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         uint32_t rs[32], rd[32];
         tmem_ld32(t_s + i * 32, rs);
         tmem_ld32(t_dp + i * 32, rd);
-        tmem_wait_ld();
+        tmem_wait_ld32(rs);
+        tmem_wait_ld32(rd);
         uint32_t pp[16], pd[16];
         // S^T and dP^T arrive with - lse / scale and - delta already added (ninth k-step of their products)
 #pragma unroll

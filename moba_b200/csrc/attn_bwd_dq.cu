@@ -45,6 +45,63 @@ struct __align__(1024) DqSmem {
   int work[8];
 };
 
+// One key tile of a compute warp (thread = query row, 32 of the tile's 128 key columns), shared by both forms of
+// the kernel: wait for S and dP of the tile, take them into registers (dP's buffer is released at once), form
+// dS = exp2(S c - lse) (dP - delta) * scale and write it over the S buffer as 16-bit pairs. `ncol` = how many of the
+// tile's key columns exist for this row. Returns false when the wait was abandoned.
+template <bool kBf16>
+__device__ __forceinline__ bool dq_compute_tile(uint64_t* bar_s, uint32_t phase_s, uint64_t* bar_dp, uint32_t phase_dp,
+                                                uint64_t* bar_dp_free, uint64_t* bar_ds, uint32_t t_s, uint32_t t_dp,
+                                                int ci, int ncol, float lse2, float dlt, float sc, float scale,
+                                                uint32_t quad_bar, const WaitCtx& wctx) {
+  const BarPhase need[2] = {{bar_s, phase_s}, {bar_dp, phase_dp}};
+  if (!__all_sync(0xffffffffu, mbar_wait_all(need, wctx))) {
+    // warps of the lane quarter that saw the barriers complete may be waiting at the quarter's barrier: release them
+    asm volatile("bar.arrive %0, 128;" ::"r"(quad_bar) : "memory");
+    return false;
+  }
+  tc_fence_after_sync();
+  const bool full = __all_sync(0xffffffffu, ncol >= 32 * ci + 32);
+  uint32_t rs[32], rd[32];
+  tmem_ld32(t_s + ci * 32, rs);
+  tmem_ld32(t_dp + ci * 32, rd);
+  tmem_wait_ld32(rs);
+  tmem_wait_ld32(rd);
+  // dP is in registers: the next tile's dP may overwrite the buffer
+  tc_fence_before_sync();
+  mbar_arrive(bar_dp_free);
+  uint32_t pd[16];
+  if (full) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
+      const float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
+      pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
+                           p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const int c0 = ci * 32 + 2 * c;
+      float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
+      float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
+      if (c0 >= ncol) p0 = 0.f;
+      if (c0 + 1 >= ncol) p1 = 0.f;
+      pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
+                           p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
+    }
+  }
+  // the 16-bit results land on TMEM columns [0, 64) of the S buffer, which other warps of the lane quarter read
+  // their fp32 inputs from: all four must have their inputs in registers first
+  asm volatile("bar.sync %0, 128;" ::"r"(quad_bar) : "memory");
+  tmem_st16(t_s + ci * 16, pd);
+  tmem_wait_st();
+  tc_fence_before_sync();
+  mbar_arrive(bar_ds);
+  return true;
+}
+
+
 template <bool kBf16, bool kGathered>
 __global__ void __launch_bounds__(kDqThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -267,56 +324,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const uint32_t quad_bar = 1 + (warp & 3);      // named barrier shared by the four warps of a lane quarter
     const float sc = a.scale * kLog2e, scale = a.scale;
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
+    for (int j = 0; j < nkv && ok; ++j) {
       const int b = j & 1;
-      const BarPhase need[2] = {{&sm.bar_s_ready[b], static_cast<uint32_t>((j >> 1) & 1)},
-                                {&sm.bar_dp_ready, static_cast<uint32_t>(j & 1)}};
-      ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
-      if (!ok) {
-        // warps of the lane quarter that saw the barriers complete may be waiting at the quarter's barrier: release them
-        asm volatile("bar.arrive %0, 128;" ::"r"(quad_bar) : "memory");
-        break;
-      }
-      tc_fence_after_sync();
       int ncol = nkeys - j * MOBA_TILE;                            // keys of this tile that exist
       if constexpr (!kGathered) ncol = min(ncol, first + row - key0 - j * MOBA_TILE + 1);   // causal: key <= query
-      const bool full = __all_sync(0xffffffffu, ncol >= 32 * ci + 32);
-      const uint32_t t_s = tmem + lane_base + b * 128u;
-      uint32_t rs[32], rd[32];
-      tmem_ld32(t_s + ci * 32, rs);
-      tmem_ld32(tm_dp + lane_base + ci * 32, rd);
-      tmem_wait_ld();
-      // dP is in registers: the next tile's dP may overwrite the buffer
-      tc_fence_before_sync();
-      mbar_arrive(&sm.bar_dp_free);
-      uint32_t pd[16];
-      if (full) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
-          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
-                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int c0 = ci * 32 + 2 * c;
-          float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
-          float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
-          if (c0 >= ncol) p0 = 0.f;
-          if (c0 + 1 >= ncol) p1 = 0.f;
-          pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
-                               p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
-        }
-      }
-      // the 16-bit results land on TMEM columns [0, 64) of the S buffer, which other warps of the lane quarter
-      // read their fp32 inputs from: all four must have their inputs in registers first
-      asm volatile("bar.sync %0, 128;" ::"r"(quad_bar) : "memory");
-      tmem_st16(t_s + ci * 16, pd);
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&sm.bar_ds_ready[b]);
+      ok = dq_compute_tile<kBf16>(&sm.bar_s_ready[b], (j >> 1) & 1, &sm.bar_dp_ready, j & 1, &sm.bar_dp_free,
+                                  &sm.bar_ds_ready[b], tmem + lane_base + b * 128u, tm_dp + lane_base, ci, ncol, lse2,
+                                  dlt, sc, scale, quad_bar, wctx);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_all_done, 0, wctx));
     // ---- epilogue: dQ rows -> global memory through shared memory, so that a warp writes whole 512-byte rows
@@ -330,7 +344,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       tc_fence_after_sync();
       uint32_t r[32];
       tmem_ld32(tm_dq + lane_base + ci * 32, r);      // each of the four threads of a row: 32 of its 128 columns
-      tmem_wait_ld();
+      tmem_wait_ld32(r);
       uint4* d = reinterpret_cast<uint4*>(stage + row * kPitch + ci * 32);
 #pragma unroll
       for (int i = 0; i < 8; ++i) d[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
@@ -776,54 +790,12 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
           row_stats(r + 1, lse2_n, dlt_n);
         }
         const int Tj = T + j, b = Tj & 1;
-        const BarPhase need[2] = {{&sm.bar_s_ready[b], static_cast<uint32_t>((Tj >> 1) & 1)},
-                                  {&sm.bar_dp_ready, static_cast<uint32_t>(Tj & 1)}};
-        ok = __all_sync(0xffffffffu, mbar_wait_all(need, wctx));
-        if (!ok) {
-          // warps of the lane quarter that saw the barriers complete may be waiting at the quarter's barrier: release them
-          asm volatile("bar.arrive %0, 128;" ::"r"(quad_bar) : "memory");
-          return false;
-        }
-        tc_fence_after_sync();
         int ncol = nkeys - j * MOBA_TILE;                            // keys of this tile that exist
         if constexpr (!kGathered) ncol = min(ncol, causal_off - j * MOBA_TILE);   // causal: key <= query
-        const bool full = __all_sync(0xffffffffu, ncol >= 32 * ci + 32);
-        const uint32_t t_s = tmem + lane_base + b * 128u;
-        uint32_t rs[32], rd[32];
-        tmem_ld32(t_s + ci * 32, rs);
-        tmem_ld32(tm_dp + lane_base + ci * 32, rd);
-        tmem_wait_ld();
-        // dP is in registers: the next tile's dP may overwrite the buffer
-        tc_fence_before_sync();
-        mbar_arrive(&sm.bar_dp_free);
-        uint32_t pd[16];
-        if (full) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
-            pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
-                                 p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int c0 = ci * 32 + 2 * c;
-            float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * c]), sc, -lse2));
-            float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * c + 1]), sc, -lse2));
-            if (c0 >= ncol) p0 = 0.f;
-            if (c0 + 1 >= ncol) p1 = 0.f;
-            pd[c] = pack2<kBf16>(p0 * fmaf(__uint_as_float(rd[2 * c]), scale, -dlt),
-                                 p1 * fmaf(__uint_as_float(rd[2 * c + 1]), scale, -dlt));
-          }
-        }
-        // the 16-bit results land on TMEM columns [0, 64) of the S buffer, which other warps of the lane quarter
-        // read their fp32 inputs from: all four must have their inputs in registers first
-        asm volatile("bar.sync %0, 128;" ::"r"(quad_bar) : "memory");
-        tmem_st16(t_s + ci * 16, pd);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(&sm.bar_ds_ready[b]);
+        if (!dq_compute_tile<kBf16>(&sm.bar_s_ready[b], (Tj >> 1) & 1, &sm.bar_dp_ready, Tj & 1, &sm.bar_dp_free,
+                                    &sm.bar_ds_ready[b], tmem + lane_base + b * 128u, tm_dp + lane_base, ci, ncol,
+                                    lse2, dlt, sc, scale, quad_bar, wctx))
+          return false;
         return true;
       };
       // The first key tile stands apart from the loop over the others: after it the previous query tile's dQ

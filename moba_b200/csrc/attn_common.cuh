@@ -62,7 +62,7 @@ __device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, uint16_t* ds
   for (int i = 0; i < 4; ++i) {
     uint32_t r[32];
     tmem_ld32(taddr + i * 32, r);
-    tmem_wait_ld();
+    tmem_wait_ld32(r);
     if (store) {
       uint32_t pk[16];
 #pragma unroll

@@ -280,7 +280,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
         for (int h = 0; h < 2; ++h) {
           uint32_t s[32];
           tmem_ld32(t_s + ch * 64 + h * 32, s);
-          tmem_wait_ld();
+          tmem_wait_ld32(s);
           if (!last) {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
@@ -331,7 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           for (int i = 0; i < 2; ++i) {
             uint32_t r[32];
             tmem_ld32(t_o + ch * 64 + i * 32, r);
-            tmem_wait_ld();
+            tmem_wait_ld32(r);
 #pragma unroll
             for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
             tmem_st32(t_o + ch * 64 + i * 32, r);
@@ -373,7 +373,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       for (int i = 0; i < 2; ++i) {
         uint32_t r[32];
         tmem_ld32(t_o + ch * 64 + i * 32, r);
-        tmem_wait_ld();
+        tmem_wait_ld32(r);
         uint32_t pk[16];
 #pragma unroll
         for (int c = 0; c < 16; ++c)

@@ -150,7 +150,7 @@ gate_topk_umma_kernel(const __grid_constant__ CUtensorMap map_q, int H, const fl
         for (int cb = 0; cb < nb; cb += 32) {
           uint32_t r[32];
           tmem_ld32(lane_addr + cb, r);
-          tmem_wait_ld();
+          tmem_wait_ld32(r);
           if (valid) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
@@ -440,7 +440,7 @@ gate_topk_stream_kernel(const __grid_constant__ CUtensorMap map_q, int H, const 
       for (int cb = 0; cb < ncand; cb += 32) {
         uint32_t r[32];
         tmem_ld32(lane_addr + cb, r);
-        tmem_wait_ld();
+        tmem_wait_ld32(r);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           const float sc = cb + c < ncand ? __uint_as_float(r[c]) : -INFINITY;
@@ -462,7 +462,7 @@ gate_topk_stream_kernel(const __grid_constant__ CUtensorMap map_q, int H, const 
         for (int cb = 0; cb < ncand; cb += 32) {
           uint32_t r[32];
           tmem_ld32(lane_addr + cb, r);
-          tmem_wait_ld();
+          tmem_wait_ld32(r);
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const float sc = __uint_as_float(r[c]);

@@ -156,7 +156,7 @@ selftest_kernel(int mode, const __grid_constant__ CUtensorMap map_a, const __gri
     for (int i = 0; i < 4; ++i) {
       uint32_t r[32];
       tmem_ld32(lane_addr + i * 32, r);
-      tmem_wait_ld();
+      tmem_wait_ld32(r);
       // mode 5 produces 64 columns; the rest of its rows is reported as zero
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -286,7 +286,7 @@ selftest_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     for (int i = 0; i < 4; ++i) {
       uint32_t r[32];
       tmem_ld32(lane_addr + i * 32, r);
-      tmem_wait_ld();
+      tmem_wait_ld32(r);
 #pragma unroll
       for (int j = 0; j < 32; ++j) s_out[row * 128 + i * 32 + j] = __uint_as_float(r[j]);
 #pragma unroll
@@ -326,7 +326,7 @@ selftest_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     for (int i = 0; i < 4; ++i) {
       uint32_t r[32];
       tmem_ld32(lane_addr + 128 + i * 32, r);
-      tmem_wait_ld();
+      tmem_wait_ld32(r);
 #pragma unroll
       for (int j = 0; j < 32; ++j) o_out[row * 128 + i * 32 + j] = __uint_as_float(r[j]);
     }
