@@ -383,10 +383,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 // causal own-chunk tiles equally often.
 constexpr int kItemSlots = 4;
 
-struct DqItem {
-  int head, first, n_rows, key0, nkeys;
-};
-
 struct __align__(1024) DqPersistSmem {
   uint8_t q[2][16384];              // [d half][128 rows x 64], 128-byte swizzle
   uint8_t d_o[2][16384];
@@ -395,7 +391,7 @@ struct __align__(1024) DqPersistSmem {
   uint64_t bar_qdo_full, bar_qdo_free, bar_k_full[kKSlots], bar_k_empty[kKSlots], bar_v_full[kVSlots],
       bar_v_empty[kVSlots], bar_s_ready[2], bar_dp_ready, bar_dp_free, bar_ds_ready[2], bar_buf_free[2],
       bar_all_done, bar_dq_free, bar_item_full[kItemSlots], bar_item_empty[kItemSlots];
-  DqItem item[kItemSlots];
+  TileItem item[kItemSlots];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -408,50 +404,6 @@ __device__ __forceinline__ void store_row_slice_f32(float* dst, const uint32_t (
                  "r"(r[8 * i + 1]), "r"(r[8 * i + 2]), "r"(r[8 * i + 3]), "r"(r[8 * i + 4]), "r"(r[8 * i + 5]),
                  "r"(r[8 * i + 6]), "r"(r[8 * i + 7])
                  : "memory");
-}
-
-// Parameters of work tile w, looked up by one full warp. `e_hint` carries the list found last time (the walk only
-// moves forward), so the search is one window of 32 offsets in the common case.
-template <bool kGathered>
-__device__ __forceinline__ DqItem dq_lookup(const BwdArgs& a, int w, int lane, int& e_hint) {
-  DqItem it;
-  if constexpr (kGathered) {
-    const int E = a.n_experts;
-    int e = e_hint;
-    while (true) {                                    // last e with work_off[e] <= w, scanning forward from the hint
-      const int idx = e + 1 + lane;
-      const bool le = idx <= E - 1 && __ldg(&a.work_off[idx]) <= w;
-      const int n_le = __popc(__ballot_sync(0xffffffffu, le));     // work_off ascends: the true lanes are a prefix
-      e += n_le;
-      if (n_le < 32) break;
-    }
-    e_hint = e;
-    const int chunk = e / a.H;
-    int val = 0;                                      // five independent loads by five lanes
-    if (lane == 0) val = __ldg(&a.list_off[e]);
-    else if (lane == 1) val = __ldg(&a.list_off[e + 1]);
-    else if (lane == 2) val = __ldg(&a.plan.chunk_start[chunk]);
-    else if (lane == 3) val = __ldg(&a.plan.chunk_start[chunk + 1]);
-    else if (lane == 4) val = __ldg(&a.work_off[e]);
-    const int l0 = __shfl_sync(0xffffffffu, val, 0), l1 = __shfl_sync(0xffffffffu, val, 1);
-    const int c0 = __shfl_sync(0xffffffffu, val, 2), c1 = __shfl_sync(0xffffffffu, val, 3);
-    const int w0 = __shfl_sync(0xffffffffu, val, 4);
-    it.head = e - chunk * a.H;
-    it.first = l0 + (w - w0) * MOBA_TILE;
-    it.n_rows = min(MOBA_TILE, l1 - it.first);
-    it.key0 = c0;
-    it.nkeys = c1 - c0;
-  } else {
-    const int nq = a.plan.n_qtiles;
-    const int t = w % nq;
-    it.head = w / nq;
-    const int chunk = __ldg(&a.plan.qtile_chunk[t]);
-    it.first = __ldg(&a.plan.qtile_start[t]);
-    it.key0 = __ldg(&a.plan.chunk_start[chunk]);
-    it.n_rows = min(MOBA_TILE, __ldg(&a.plan.chunk_start[chunk + 1]) - it.first);
-    it.nkeys = it.first + it.n_rows - it.key0;       // causal: keys up to the last row of the tile
-  }
-  return it;
 }
 
 template <bool kBf16, bool kGathered>
@@ -508,7 +460,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const uint32_t tm_dp = tmem + 256, tm_dq = tmem + 384;
 
   // a consuming warp's copy of the parameters of round r (published by the producer warp)
-  auto take_item = [&](int r, DqItem& it) -> bool {
+  auto take_item = [&](int r, TileItem& it) -> bool {
     const int slot = r & (kItemSlots - 1);
     if (!__all_sync(0xffffffffu, mbar_wait(&sm.bar_item_full[slot], static_cast<uint32_t>((r / kItemSlots) & 1), wctx)))
       return false;
@@ -529,7 +481,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       if (r >= kItemSlots)
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_item_empty[slot], static_cast<uint32_t>((r / kItemSlots - 1) & 1), wctx));
       if (!ok) break;
-      const DqItem it = dq_lookup<kGathered>(a, w, lane, e_hint);
+      const TileItem it = lookup_tile<kGathered>(a, w, lane, e_hint);
       const int nkv = (it.nkeys + MOBA_TILE - 1) / MOBA_TILE;
       if (lane == 0) {
         sm.item[slot] = it;
@@ -582,7 +534,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     int T = 0;
     for (int r = 0; r < n_rounds && ok; ++r) {
       if (item_of_round(r) >= n_items) break;
-      DqItem it;
+      TileItem it;
       ok = take_item(r, it);
       if (!ok) break;
       const int nkv = (it.nkeys + MOBA_TILE - 1) / MOBA_TILE;
@@ -619,7 +571,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     int T = 0;
     for (int r = 0; r < n_rounds && ok; ++r) {
       if (item_of_round(r) >= n_items) break;
-      DqItem it;
+      TileItem it;
       ok = take_item(r, it);
       if (!ok) break;
       const int nkv = (it.nkeys + MOBA_TILE - 1) / MOBA_TILE;
@@ -656,7 +608,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     int T = 0;
     for (int r = 0; r < n_rounds && ok; ++r) {
       if (item_of_round(r) >= n_items) break;
-      DqItem it;
+      TileItem it;
       ok = take_item(r, it);
       if (!ok) break;
       const int nkv = (it.nkeys + MOBA_TILE - 1) / MOBA_TILE;
@@ -701,7 +653,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     };
     // log-sum-exp (log2 units) and delta * scale of the thread's row in the tile of round r; padding rows: exp2(-inf) = 0
     auto row_stats = [&](int r, float& lse2, float& dlt) {
-      const DqItem& it = sm.item[r & (kItemSlots - 1)];
+      const TileItem& it = sm.item[r & (kItemSlots - 1)];
       lse2 = INFINITY;
       dlt = 0.f;
       if (row < it.n_rows) {
@@ -724,7 +676,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       tmem_wait_ld32(rq);
       tc_fence_before_sync();
       mbar_arrive(&sm.bar_dq_free);          // the accumulator may be overwritten by the next tile's first product
-      const DqItem& it = sm.item[r & (kItemSlots - 1)];
+      const TileItem& it = sm.item[r & (kItemSlots - 1)];
       const int n_rows = it.n_rows;
       const int row0 = (row & ~3);             // first row of the quad
       size_t off, pitch;

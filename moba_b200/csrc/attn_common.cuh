@@ -35,6 +35,55 @@ struct BwdArgs {
   float scale;           // softmax scale (head_dim^-0.5 of the caller's head dim)
 };
 
+// One 128-row query tile of a persistent kernel's walk: a (chunk, head) list tile or an own-chunk tile.
+struct TileItem {
+  int head, first, n_rows, key0, nkeys;
+};
+
+// Parameters of work tile w, looked up by one full warp. `e_hint` carries the list found last time (the walk only
+// moves forward), so the search is one window of 32 offsets in the common case.
+template <bool kGathered, typename Args>
+__device__ __forceinline__ TileItem lookup_tile(const Args& a, int w, int lane, int& e_hint) {
+  TileItem it;
+  if constexpr (kGathered) {
+    const int E = a.n_experts;
+    int e = e_hint;
+    while (true) {                                    // last e with work_off[e] <= w, scanning forward from the hint
+      const int idx = e + 1 + lane;
+      const bool le = idx <= E - 1 && __ldg(&a.work_off[idx]) <= w;
+      const int n_le = __popc(__ballot_sync(0xffffffffu, le));     // work_off ascends: the true lanes are a prefix
+      e += n_le;
+      if (n_le < 32) break;
+    }
+    e_hint = e;
+    const int chunk = e / a.H;
+    int val = 0;                                      // five independent loads by five lanes
+    if (lane == 0) val = __ldg(&a.list_off[e]);
+    else if (lane == 1) val = __ldg(&a.list_off[e + 1]);
+    else if (lane == 2) val = __ldg(&a.plan.chunk_start[chunk]);
+    else if (lane == 3) val = __ldg(&a.plan.chunk_start[chunk + 1]);
+    else if (lane == 4) val = __ldg(&a.work_off[e]);
+    const int l0 = __shfl_sync(0xffffffffu, val, 0), l1 = __shfl_sync(0xffffffffu, val, 1);
+    const int c0 = __shfl_sync(0xffffffffu, val, 2), c1 = __shfl_sync(0xffffffffu, val, 3);
+    const int w0 = __shfl_sync(0xffffffffu, val, 4);
+    it.head = e - chunk * a.H;
+    it.first = l0 + (w - w0) * MOBA_TILE;
+    it.n_rows = min(MOBA_TILE, l1 - it.first);
+    it.key0 = c0;
+    it.nkeys = c1 - c0;
+  } else {
+    const int nq = a.plan.n_qtiles;
+    const int t = w % nq;
+    it.head = w / nq;
+    const int chunk = __ldg(&a.plan.qtile_chunk[t]);
+    it.first = __ldg(&a.plan.qtile_start[t]);
+    it.key0 = __ldg(&a.plan.chunk_start[chunk]);
+    it.n_rows = min(MOBA_TILE, __ldg(&a.plan.chunk_start[chunk + 1]) - it.first);
+    it.nkeys = it.first + it.n_rows - it.key0;       // causal: keys up to the last row of the tile
+  }
+  return it;
+}
+
 // `nthreads` (a multiple of 16, at most 128) threads copy 128 rows x 256 B (row i from token row_tok[i], head
 // `head`) into two swizzled [128 x 64] sub-tiles at dst / dst + 16384; rows with a negative token are
 // zero-filled. `t` is the thread's index inside the copying group.
