@@ -5,7 +5,7 @@ the shapes the reference's own speed test uses and on a 4-head cut of the 131072
 reference's tests/test_moba_speedup.py:45-76 (3 warm-up + 10 timed iterations, wall clock around a device
 synchronise), with this package timed the same way beside it and the largest difference between the two results.
 
-    python -m baseline.reference_on_b200 [--probe] [--out gpurun_out/reference_on_b200.json]
+    python -m baseline.reference_on_b200 [--probe] [--out reference_on_b200.json]
 
 Prints one JSON object; {"unavailable": "<reason>"} when the reference cannot run here. Test / benchmark
 infrastructure: nothing in the product package imports it.
