@@ -380,10 +380,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.bar_all_done, 0, wctx));
     if (ok) {
       tc_fence_after_sync();
-      const bool store = row < n_keys;
-      const size_t off = (static_cast<size_t>(kv0 + row) * H_kv + head_kv) * MOBA_HEAD_DIM;
-      if (ci == 0) store_row_from_tmem<kBf16>(tm_dk + lane_base, a.o0 + off, store);
-      else store_row_from_tmem<kBf16>(tm_dv + lane_base, a.o1 + off, store);
+      // warps 0-3 write dK, warps 4-7 dV: thread = key row, whole 128-byte lines per quad of rows
+      const int row0 = row & ~3;
+      const size_t off = (static_cast<size_t>(kv0 + row0) * H_kv + head_kv) * MOBA_HEAD_DIM;
+      const size_t pitch = static_cast<size_t>(H_kv) * MOBA_HEAD_DIM;
+      if (ci == 0) store_rows_from_tmem<kBf16>(tm_dk + lane_base, a.o0 + off, pitch, n_keys - row0, lane);
+      else store_rows_from_tmem<kBf16>(tm_dv + lane_base, a.o1 + off, pitch, n_keys - row0, lane);
     }
   }
   tc_fence_before_sync();

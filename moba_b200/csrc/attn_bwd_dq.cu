@@ -688,32 +688,9 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         pitch = static_cast<size_t>(a.H) * MOBA_HEAD_DIM;
       }
       // A thread holds 32 consecutive columns (four 32-byte pieces) of its row; the four lanes of a quad swap pieces
-      // so that each store instruction writes whole 128-byte lines (lane a: piece a of the quad's row i in store i)
-      // instead of 32 bytes to each of 32 lines.
-#pragma unroll
-      for (int bit = 1; bit <= 2; bit <<= 1) {
-        const bool up = (lane & bit) != 0;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c & bit) continue;               // pieces c (bit clear) and c | bit (bit set) form a pair
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            const uint32_t lo = rq[8 * c + x], hi = rq[8 * (c | bit) + x];
-            const uint32_t got = __shfl_xor_sync(0xffffffffu, up ? lo : hi, bit);
-            rq[8 * c + x] = up ? got : lo;
-            rq[8 * (c | bit) + x] = up ? hi : got;
-          }
-        }
-      }
-      float* dst = a.dq_f32 + off + ci * 32 + (lane & 3) * 8;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (row0 + i < n_rows)
-          asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + i * pitch),
-                       "r"(rq[8 * i]), "r"(rq[8 * i + 1]), "r"(rq[8 * i + 2]), "r"(rq[8 * i + 3]), "r"(rq[8 * i + 4]),
-                       "r"(rq[8 * i + 5]), "r"(rq[8 * i + 6]), "r"(rq[8 * i + 7])
-                       : "memory");
-      }
+      // so that each store instruction writes whole 128-byte lines instead of 32 bytes to each of 32 lines.
+      quad_transpose_pieces(rq, lane);
+      store_quad_rows(a.dq_f32 + off + ci * 32 + (lane & 3) * 8, pitch, n_rows - row0, rq);
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.bar_item_empty[r & (kItemSlots - 1)]);
       return true;

@@ -102,23 +102,59 @@ __device__ __forceinline__ void gather_rows(uint8_t* dst, const uint16_t* src, c
   }
 }
 
-// One TMEM lane (128 fp32 columns starting at taddr) -> one 16-bit row in global memory. The loads are
-// warp-collective, so every lane executes them; only `store` lanes write.
-template <bool kBf16>
-__device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, uint16_t* dst_row, bool store) {
-  uint4* dst = reinterpret_cast<uint4*>(dst_row);
+// Four 32-byte pieces per lane (r[8 p .. 8 p + 7] = piece p of the lane's row) are swapped inside each quad of
+// lanes, so that afterwards lane a holds piece a of the quad's row i in slot i: a store of slot i then writes whole
+// 128-byte lines (four lanes x 32 bytes of one row) instead of 32 bytes to each of 32 lines.
+__device__ __forceinline__ void quad_transpose_pieces(uint32_t (&r)[32], int lane) {
+#pragma unroll
+  for (int bit = 1; bit <= 2; bit <<= 1) {
+    const bool up = (lane & bit) != 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (c & bit) continue;               // pieces c (bit clear) and c | bit (bit set) form a pair
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const uint32_t lo = r[8 * c + x], hi = r[8 * (c | bit) + x];
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, up ? lo : hi, bit);
+        r[8 * c + x] = up ? got : lo;
+        r[8 * (c | bit) + x] = up ? hi : got;
+      }
+    }
+  }
+}
+// Slot i of every lane (after quad_transpose_pieces) -> row i of the quad: dst = the lane's 32-byte piece of the
+// quad's first row, pitch = elements of T between consecutive rows, n_valid = rows of the quad that exist.
+template <typename T>
+__device__ __forceinline__ void store_quad_rows(T* dst, size_t pitch, int n_valid, const uint32_t (&r)[32]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint32_t r[32];
-    tmem_ld32(taddr + i * 32, r);
-    tmem_wait_ld32(r);
-    if (store) {
-      uint32_t pk[16];
+    if (i < n_valid)
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + i * pitch), "r"(r[8 * i]),
+                   "r"(r[8 * i + 1]), "r"(r[8 * i + 2]), "r"(r[8 * i + 3]), "r"(r[8 * i + 4]), "r"(r[8 * i + 5]),
+                   "r"(r[8 * i + 6]), "r"(r[8 * i + 7])
+                   : "memory");
+  }
+}
+
+// The 128 TMEM lanes of a tile (thread = row, 128 fp32 columns starting at taddr) -> 16-bit rows in global memory,
+// written as whole 128-byte lines. `quad_dst` = column 0 of the first row of this lane's quad, `pitch` = elements
+// between consecutive rows, `n_valid` = rows of the quad that exist (<= 0: none). Warp-collective.
+template <bool kBf16>
+__device__ __forceinline__ void store_rows_from_tmem(uint32_t taddr, uint16_t* quad_dst, size_t pitch, int n_valid,
+                                                     int lane) {
 #pragma unroll
-      for (int c = 0; c < 16; ++c) pk[c] = pack2<kBf16>(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1]));
+  for (int half = 0; half < 2; ++half) {
+    uint32_t pk[32];                       // 64 columns as 16-bit pairs: four 32-byte pieces
 #pragma unroll
-      for (int g = 0; g < 4; ++g) dst[i * 4 + g] = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+    for (int i = 0; i < 2; ++i) {
+      uint32_t r[32];
+      tmem_ld32(taddr + half * 64 + i * 32, r);
+      tmem_wait_ld32(r);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) pk[i * 16 + c] = pack2<kBf16>(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1]));
     }
+    quad_transpose_pieces(pk, lane);
+    store_quad_rows(quad_dst + half * 64 + (lane & 3) * 16, pitch, n_valid, pk);
   }
 }
 
