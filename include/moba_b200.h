@@ -160,6 +160,16 @@ int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_
                      int32_t* row_of, int32_t* status, int32_t device, void* stream);
 
 /*
+ * One record per 128-row work tile w of the list part (w < max_work_tiles_per_head * H, the grid the list kernels
+ * run on): tile_rec[8 w ..] = {head, first list row, rows (0: no such tile), first key token of the chunk, keys in
+ * the chunk, 0, 0, 0}, from list_off / work_off of moba_build_lists. Part of the list building (the reference's
+ * index_select / split bookkeeping, moba/moba_efficient.py:375-423): the tile kernels that receive the records
+ * start from one 32-byte load instead of a search through work_off. tile_rec: [max_work_tiles_per_head * H, 8] int32.
+ */
+int moba_tile_records(int32_t H, const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
+                      const int32_t* work_off, int32_t* tile_rec, int32_t device, void* stream);
+
+/*
  * Forward attention tiles (tcgen05 / TMEM, TMA-fed K and V, online softmax). Replaces the two
  * _flash_attn_varlen_forward calls of MixedAttention.forward (moba/moba_efficient.py:89-116) and the Q / KV
  * regrouping that feeds them (:381-386, :406-414).
@@ -174,12 +184,14 @@ int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_
  * parts (here and in the two backward tile entry points): 3 = both parts (the normal call), 1 = own-chunk part
  * only, 2 = list part only -- the two halves MixedAttention (moba/moba_efficient.py:67-267) runs as separate
  * flash calls; buffers of a part that is not requested may be NULL.
+ * tile_rec (here, in moba_gather_rows and in moba_attn_bwd_dq): the work-tile records of moba_tile_records, or NULL
+ * (the kernels then find a tile's list by searching work_off).
  */
 int moba_attn_fwd(const void* q, const void* k, const void* v, int32_t dtype, int32_t H, int64_t stride_s,
                   int64_t stride_h, const moba_kv_layout* kv, const moba_plan_info* info, const int32_t* meta_dev,
-                  const int32_t* list_off, const int32_t* work_off, const int32_t* list_tok, void* out,
-                  float* lse, void* part_o, float* part_lse, int32_t parts, float softmax_scale, int32_t* status,
-                  int32_t device, void* stream);
+                  const int32_t* list_off, const int32_t* work_off, const int32_t* list_tok,
+                  const int32_t* tile_rec, void* out, float* lse, void* part_o, float* part_lse, int32_t parts,
+                  float softmax_scale, int32_t* status, int32_t device, void* stream);
 
 /*
  * Log-sum-exp merge of the self result with the <= kk gathered partial results of every (token, head),
@@ -201,8 +213,9 @@ int moba_bwd_delta(const void* out, const void* d_out, int32_t dtype, int32_t H,
  */
 int moba_gather_rows(const void* q, const void* d_out, const float* lse, const float* delta, int32_t dtype,
                      int32_t H, int64_t stride_s, int64_t stride_h, const moba_plan_info* info,
-                     const int32_t* list_off, const int32_t* work_off, const int32_t* list_tok, void* qg,
-                     void* dog, float* lse_g, float* delta_g, int32_t device, void* stream);
+                     const int32_t* list_off, const int32_t* work_off, const int32_t* list_tok,
+                     const int32_t* tile_rec, void* qg, void* dog, float* lse_g, float* delta_g, int32_t device,
+                     void* stream);
 
 /*
  * Backward, key/value side: dk, dv [S, kv_heads, D] (dtype of q; kv_heads == H without a kv layout). One CTA
@@ -232,8 +245,8 @@ int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* 
 int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype,
                      int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                      const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off, const int32_t* work_off,
-                     const int32_t* list_tok, const void* qg, const void* dog, const float* lse_g,
-                     const float* delta_g, const float* lse, const float* delta, float* dq_self,
+                     const int32_t* list_tok, const int32_t* tile_rec, const void* qg, const void* dog,
+                     const float* lse_g, const float* delta_g, const float* lse, const float* delta, float* dq_self,
                      float* part_dq, int32_t parts, float softmax_scale, int32_t* status, int32_t device,
                      void* stream);
 

@@ -72,15 +72,16 @@ SIGNATURES = {
     "moba_pool_keys_static": (ctypes.c_int, [_P, _I32, _I32, _I64, _I64, _INFO, _P, _P, _I32, _P]),
     "moba_gate_topk": (ctypes.c_int, [_P, _I32, _I32, _I64, _I64, _P, _I32, _INFO, _P, _P, _P, _P, _P, _I32, _P]),
     "moba_build_lists": (ctypes.c_int, [_I32, _INFO, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _P]),
-    "moba_attn_fwd": (ctypes.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P,
+    "moba_tile_records": (ctypes.c_int, [_I32, _INFO, _P, _P, _P, _P, _I32, _P]),
+    "moba_attn_fwd": (ctypes.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P, _P,
                                      _P, _I32, _F32, _P, _I32, _P]),
     "moba_merge_fwd": (ctypes.c_int, [_P, _P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),
     "moba_bwd_delta": (ctypes.c_int, [_P, _P, _I32, _I32, _I64, _P, _I32, _P]),
-    "moba_gather_rows": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _INFO, _P, _P, _P, _P, _P, _P, _P,
+    "moba_gather_rows": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _INFO, _P, _P, _P, _P, _P, _P, _P, _P,
                                         _I32, _P]),
     "moba_attn_bwd_dkdv": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P,
                                           _P, _P, _P, _P, _I32, _F32, _P, _I32, _P]),
-    "moba_attn_bwd_dq": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P,
+    "moba_attn_bwd_dq": (ctypes.c_int, [_P, _P, _P, _P, _I32, _I32, _I64, _I64, _KV, _INFO, _P, _P, _P, _P, _P, _P, _P,
                                         _P, _P, _P, _P, _P, _P, _I32, _F32, _P, _I32, _P]),
     "moba_memcpy_2d": (ctypes.c_int, [_P, _I64, _P, _I64, _I64, _I64, _I32, _I32, _P]),
     "moba_merge_dq": (ctypes.c_int, [_P, _I32, _I32, _INFO, _P, _P, _P, _I32, _P]),

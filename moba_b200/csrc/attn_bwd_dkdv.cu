@@ -441,7 +441,7 @@ extern "C" int moba_attn_bwd_dkdv(const void* q, const void* k, const void* v, c
   a.d_out = static_cast<const uint16_t*>(d_out);
   a.stride_s = stride_s; a.stride_h = stride_h; a.H = H;
   a.plan = make_plan_dev(info, meta_dev);
-  a.list_off = list_off; a.work_off = nullptr; a.list_tok = nullptr;
+  a.list_off = list_off; a.work_off = nullptr; a.list_tok = nullptr; a.tile_rec = nullptr;
   a.lse = lse; a.delta = delta;
   a.o0 = static_cast<uint16_t*>(dk); a.o1 = static_cast<uint16_t*>(dv); a.dq_f32 = nullptr;
   a.status = status;

@@ -116,13 +116,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   if (warp == 0) {
     int chunk = 0, head = 0, first = 0, n_rows = 0, key0 = 0, nkeys = 0, active = 1;
     if constexpr (kGathered) {
-      // which (chunk, head) list owns work tile w: the last e with work_off[e] <= w. A 32-way search, every
-      // lane probing one entry per round (two dependent loads for up to 1024 lists instead of ten).
       const int w = blockIdx.x;
       const int E = a.n_experts;
-      if (w >= a.work_off[E]) {
+      if (a.tile_rec) {
+        // the tile's record: one 32-byte load (lanes 0-7) instead of the search below
+        const int val = lane < 8 ? __ldg(&a.tile_rec[8 * static_cast<size_t>(w) + lane]) : 0;
+        head = __shfl_sync(0xffffffffu, val, 0);
+        first = __shfl_sync(0xffffffffu, val, 1);
+        n_rows = __shfl_sync(0xffffffffu, val, 2);
+        key0 = __shfl_sync(0xffffffffu, val, 3);
+        nkeys = __shfl_sync(0xffffffffu, val, 4);
+        active = n_rows > 0;
+      } else if (w >= a.work_off[E]) {
         active = 0;
       } else {
+        // which (chunk, head) list owns work tile w: the last e with work_off[e] <= w. A 32-way search, every
+        // lane probing one entry per round (two dependent loads for up to 1024 lists instead of ten).
         int lo = 0, hi = E;
         while (hi - lo > 1) {
           const int step = (hi - lo + 31) / 32;
@@ -752,7 +761,7 @@ attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, const void* d_out, int32_t dtype,
                                 int32_t H, int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                                 const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
-                                const int32_t* work_off, const int32_t* list_tok, const void* qg, const void* dog, const float* lse_g,
+                                const int32_t* work_off, const int32_t* list_tok, const int32_t* tile_rec, const void* qg, const void* dog, const float* lse_g,
                                 const float* delta_g, const float* lse, const float* delta, float* dq,
                                 float* part_dq, int32_t parts, float softmax_scale, int32_t* status, int32_t device,
                                 void* stream) {
@@ -794,7 +803,7 @@ extern "C" int moba_attn_bwd_dq(const void* q, const void* k, const void* v, con
   a.stride_s = stride_s; a.stride_h = stride_h; a.H = H; a.lse_g = lse_g; a.delta_g = delta_g; a.parts = parts;
   a.scale = softmax_scale_or_default(softmax_scale);
   a.plan = make_plan_dev(info, meta_dev);
-  a.list_off = list_off; a.work_off = work_off; a.list_tok = list_tok;
+  a.list_off = list_off; a.work_off = work_off; a.list_tok = list_tok; a.tile_rec = tile_rec;
   a.lse = lse; a.delta = delta;
   a.o0 = nullptr; a.o1 = nullptr; a.dq_f32 = dq;
   a.status = status;

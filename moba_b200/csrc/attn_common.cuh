@@ -21,6 +21,7 @@ struct BwdArgs {
   const int32_t* list_off;
   const int32_t* work_off;
   const int32_t* list_tok;
+  const int32_t* tile_rec;   // work-tile records (moba_tile_records), or null: search work_off
   const float* lse;      // [S,H] merged log-sum-exp (natural log)
   const float* delta;    // [S,H] rowsum(dO * O)
   const float* lse_g;    // dkdv: lse / delta of the list rows, in list order [R*H]
@@ -46,6 +47,15 @@ template <bool kGathered, typename Args>
 __device__ __forceinline__ TileItem lookup_tile(const Args& a, int w, int lane, int& e_hint) {
   TileItem it;
   if constexpr (kGathered) {
+    if (a.tile_rec) {
+      const int val = lane < 8 ? __ldg(&a.tile_rec[8 * static_cast<size_t>(w) + lane]) : 0;
+      it.head = __shfl_sync(0xffffffffu, val, 0);
+      it.first = __shfl_sync(0xffffffffu, val, 1);
+      it.n_rows = __shfl_sync(0xffffffffu, val, 2);
+      it.key0 = __shfl_sync(0xffffffffu, val, 3);
+      it.nkeys = __shfl_sync(0xffffffffu, val, 4);
+      return it;
+    }
     const int E = a.n_experts;
     int e = e_hint;
     while (true) {                                    // last e with work_off[e] <= w, scanning forward from the hint

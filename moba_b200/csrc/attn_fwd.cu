@@ -63,6 +63,7 @@ struct FwdArgs {
   const int32_t* list_off;
   const int32_t* work_off;
   const int32_t* list_tok;
+  const int32_t* tile_rec;   // work-tile records (moba_tile_records), or null: search work_off
   uint16_t* out;        // self: [S,H,D] contiguous; gathered: part_o [R*H, D]
   float* lse;           // self: [S,H]; gathered: part_lse [R*H]
   int* status;
@@ -84,13 +85,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   if (warp == 0) {
     int chunk = 0, head = 0, first = 0, n_rows = 0, nkv = 0, key0 = 0, nkeys = 0, active = 1;
     if constexpr (kGathered) {
-      // which (chunk, head) list owns work tile w: the last e with work_off[e] <= w. A 32-way search, every
-      // lane probing one entry per round (three dependent loads for 30000 lists instead of fifteen).
       const int w = blockIdx.x;
       const int E = a.n_experts;
-      if (w >= a.work_off[E]) {
+      if (a.tile_rec) {
+        // the tile's record: one 32-byte load (lanes 0-7) instead of the search below
+        const int val = lane < 8 ? __ldg(&a.tile_rec[8 * static_cast<size_t>(w) + lane]) : 0;
+        head = __shfl_sync(0xffffffffu, val, 0);
+        first = __shfl_sync(0xffffffffu, val, 1);
+        n_rows = __shfl_sync(0xffffffffu, val, 2);
+        key0 = __shfl_sync(0xffffffffu, val, 3);
+        nkeys = __shfl_sync(0xffffffffu, val, 4);
+        nkv = (nkeys + MOBA_TILE - 1) / MOBA_TILE;
+        active = n_rows > 0;
+      } else if (w >= a.work_off[E]) {
         active = 0;
       } else {
+        // which (chunk, head) list owns work tile w: the last e with work_off[e] <= w. A 32-way search, every
+        // lane probing one entry per round (three dependent loads for 30000 lists instead of fifteen).
         int lo = 0, hi = E;
         while (hi - lo > 1) {
           const int step = (hi - lo + 31) / 32;
@@ -432,9 +443,9 @@ int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mv, FwdArgs args, const
 extern "C" int moba_attn_fwd(const void* q, const void* k, const void* v, int32_t dtype, int32_t H,
                              int64_t stride_s, int64_t stride_h, const moba_kv_layout* kv,
                              const moba_plan_info* info, const int32_t* meta_dev, const int32_t* list_off,
-                             const int32_t* work_off, const int32_t* list_tok, void* out, float* lse,
-                             void* part_o, float* part_lse, int32_t parts, float softmax_scale, int32_t* status,
-                             int32_t device, void* stream) {
+                             const int32_t* work_off, const int32_t* list_tok, const int32_t* tile_rec, void* out,
+                             float* lse, void* part_o, float* part_lse, int32_t parts, float softmax_scale,
+                             int32_t* status, int32_t device, void* stream) {
   using namespace moba;
   int rc = check_common(q, H, stride_s, stride_h, info, meta_dev);
   if (rc) return rc;
@@ -458,6 +469,7 @@ extern "C" int moba_attn_fwd(const void* q, const void* k, const void* v, int32_
   a.list_off = list_off;
   a.work_off = work_off;
   a.list_tok = list_tok;
+  a.tile_rec = tile_rec;
   a.out = static_cast<uint16_t*>(out);
   a.lse = lse;
   a.status = status;

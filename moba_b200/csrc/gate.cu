@@ -345,6 +345,51 @@ extern "C" int moba_gate_topk(const void* q, int32_t dtype, int32_t H, int64_t s
   }
 }
 
+namespace moba {
+namespace {
+// One record per work tile: the list that owns it (last e with work_off[e] <= w), the tile's first row and row count,
+// the key range of the list's chunk. Tiles past the last one get zero rows.
+__global__ void __launch_bounds__(256)
+tile_records_kernel(int H, PlanDev plan, int n_experts, int n_tiles, const int32_t* __restrict__ list_off,
+                    const int32_t* __restrict__ work_off, int32_t* __restrict__ tile_rec) {
+  const int w = blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= n_tiles) return;
+  int4 lo4 = make_int4(0, 0, 0, 0), hi4 = make_int4(0, 0, 0, 0);
+  if (w < work_off[n_experts]) {
+    int lo = 0, hi = n_experts;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (work_off[mid] <= w) lo = mid; else hi = mid;
+    }
+    const int chunk = lo / H;
+    const int first = list_off[lo] + (w - work_off[lo]) * MOBA_TILE;
+    const int key0 = plan.chunk_start[chunk];
+    lo4 = make_int4(lo - chunk * H, first, min(MOBA_TILE, list_off[lo + 1] - first), key0);
+    hi4 = make_int4(plan.chunk_start[chunk + 1] - key0, 0, 0, 0);
+  }
+  reinterpret_cast<int4*>(tile_rec)[2 * w] = lo4;
+  reinterpret_cast<int4*>(tile_rec)[2 * w + 1] = hi4;
+}
+}  // namespace
+}  // namespace moba
+
+extern "C" int moba_tile_records(int32_t H, const moba_plan_info* info, const int32_t* meta_dev,
+                                 const int32_t* list_off, const int32_t* work_off, int32_t* tile_rec, int32_t device,
+                                 void* stream) {
+  using namespace moba;
+  MOBA_REQUIRE(info && meta_dev && list_off && work_off && tile_rec, MOBA_ERR_ARG, "null pointer argument");
+  MOBA_REQUIRE(H >= 1 && H <= 65535, MOBA_ERR_ARG, "H=%d out of range", H);
+  const int64_t nw = info->max_work_tiles_per_head * H;
+  MOBA_REQUIRE(nw < (1ll << 28), MOBA_ERR_LIMIT, "too many gathered tiles");
+  MOBA_SET_DEVICE(device);
+  if (info->kk == 0 || nw == 0) return 0;
+  const PlanDev plan = make_plan_dev(info, meta_dev);
+  tile_records_kernel<<<static_cast<unsigned>((nw + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      H, plan, info->n_chunks * H, static_cast<int>(nw), list_off, work_off, tile_rec);
+  MOBA_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int moba_build_lists(int32_t H, const moba_plan_info* info, const int32_t* meta_dev,
                                 const int32_t* sel, int32_t* tile_cnt, int32_t* list_off, int32_t* work_off,
                                 int32_t* list_tok, int32_t* row_of, int32_t* status, int32_t device,

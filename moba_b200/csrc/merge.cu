@@ -195,12 +195,19 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ d_out, const float* __restrict__ lse,
                    const float* __restrict__ delta, int H, int64_t stride_s, int64_t stride_h, int n_experts,
                    const int32_t* __restrict__ list_off, const int32_t* __restrict__ work_off,
-                   const int32_t* __restrict__ list_tok, uint16_t* __restrict__ qg, uint16_t* __restrict__ dog,
-                   float* __restrict__ lse_g, float* __restrict__ delta_g) {
+                   const int32_t* __restrict__ list_tok, const int32_t* __restrict__ tile_rec,
+                   uint16_t* __restrict__ qg, uint16_t* __restrict__ dog, float* __restrict__ lse_g,
+                   float* __restrict__ delta_g) {
   __shared__ int s_work[3];
   if (threadIdx.x == 0) {
     const int w = blockIdx.x;
-    if (w >= work_off[n_experts]) {
+    if (tile_rec) {
+      // the tile's record (moba_tile_records) instead of the search below
+      const int4 rec = __ldg(reinterpret_cast<const int4*>(tile_rec) + 2 * static_cast<size_t>(w));
+      s_work[0] = rec.x;
+      s_work[1] = rec.y;
+      s_work[2] = rec.z;
+    } else if (w >= work_off[n_experts]) {
       s_work[2] = 0;
     } else {
       int lo = 0, hi = n_experts;          // last e with work_off[e] <= w
@@ -311,8 +318,8 @@ extern "C" int moba_merge_dq(void* dq, int32_t dtype, int32_t H, const moba_plan
 extern "C" int moba_gather_rows(const void* q, const void* d_out, const float* lse, const float* delta,
                                 int32_t dtype, int32_t H, int64_t stride_s, int64_t stride_h,
                                 const moba_plan_info* info, const int32_t* list_off, const int32_t* work_off,
-                                const int32_t* list_tok, void* qg, void* dog, float* lse_g, float* delta_g,
-                                int32_t device, void* stream) {
+                                const int32_t* list_tok, const int32_t* tile_rec, void* qg, void* dog, float* lse_g,
+                                float* delta_g, int32_t device, void* stream) {
   using namespace moba;
   MOBA_REQUIRE(q && d_out && lse && delta && info && list_off && work_off && list_tok && qg && dog && lse_g && delta_g,
                MOBA_ERR_ARG, "null pointer argument");
@@ -324,8 +331,8 @@ extern "C" int moba_gather_rows(const void* q, const void* d_out, const float* l
   MOBA_REQUIRE(nw < (1ll << 31), MOBA_ERR_LIMIT, "too many gathered tiles");
   gather_rows_kernel<<<static_cast<unsigned>(nw), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(d_out), lse, delta, H, stride_s, stride_h,
-      info->n_chunks * H, list_off, work_off, list_tok, static_cast<uint16_t*>(qg), static_cast<uint16_t*>(dog),
-      lse_g, delta_g);
+      info->n_chunks * H, list_off, work_off, list_tok, tile_rec, static_cast<uint16_t*>(qg),
+      static_cast<uint16_t*>(dog), lse_g, delta_g);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -106,7 +106,7 @@ def _forward(q, k, v, cu_seqlens, moba_chunk_size, moba_topk, out=None, scale=0.
         kmean = ops.pool_keys(kg, plan)
         sel, _, tile_cnt = ops.gate_topk(qg, kmean, plan, status=status)
         list_off, work_off, list_tok, row_of = ops.build_lists(plan, H, sel, tile_cnt, status=status)
-        lists = (list_off, work_off, list_tok)
+        lists = (list_off, work_off, list_tok, ops.tile_records(plan, H, list_off, work_off))
     else:
         # moba_topk == 1 or every sequence is a single chunk: plain causal attention over whole sequences
         # (moba/moba_efficient.py:314-321) = self-chunk attention with one chunk per sequence

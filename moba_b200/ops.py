@@ -262,6 +262,25 @@ def build_lists(plan, H, sel, tile_cnt, status=None):
     return list_off, work_off, list_tok, row_of
 
 
+def tile_records(plan, H, list_off, work_off):
+    """[max_work_tiles * H, 8] int32: one record per 128-row work tile of the list part (head, first row, rows, first
+    key token, keys), so that the tile kernels start from one load instead of a search through work_off. Optional:
+    a `lists` tuple may carry it as its fourth element."""
+    n = max(int(plan.info.max_work_tiles_per_head) * H, 1)
+    rec = torch.empty((n, 8), dtype=torch.int32, device=list_off.device)
+    with _timed("build_lists", list_off.device):
+        call("moba_tile_records", H, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off),
+             _ptr(rec), _dev_index(list_off), _stream(list_off.device))
+    return rec
+
+
+def _split_lists(lists):
+    """(list_off, work_off, list_tok, tile_rec or None) from a 3- or 4-element `lists` tuple."""
+    if len(lists) == 4:
+        return lists
+    return (*lists, None)
+
+
 def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None, scale=0.0):
     """Self-chunk causal attention -> (out, lse); gathered rows -> (part_o, part_lse).
 
@@ -271,7 +290,7 @@ def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None, scale=0.0):
         _check_shd(n, t)
     S, H, D = q.shape
     kv = _kv_layout(q, k, v)
-    list_off, work_off, list_tok = lists
+    list_off, work_off, list_tok, tile_rec = _split_lists(lists)
     if out is None:
         out = torch.empty((S, H, D), dtype=q.dtype, device=q.device)
     elif out.shape != (S, H, D) or out.dtype != q.dtype or not out.is_contiguous():
@@ -282,8 +301,9 @@ def attn_fwd(q, k, v, plan, lists, status, parts=3, out=None, scale=0.0):
     part_lse = torch.empty(R, dtype=torch.float32, device=q.device)
     with _timed("attn_fwd", q.device):
         call("moba_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _DTYPES[q.dtype], H, q.stride(0), q.stride(1), kv,
-             ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(out),
-             _ptr(lse), _ptr(part_o), _ptr(part_lse), parts, float(scale), _ptr(status), _dev_index(q), _stream(q.device))
+             ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(tile_rec),
+             _ptr(out), _ptr(lse), _ptr(part_o), _ptr(part_lse), parts, float(scale), _ptr(status), _dev_index(q),
+             _stream(q.device))
     return out, lse, part_o, part_lse
 
 
@@ -306,7 +326,7 @@ def bwd_delta(out, d_out):
 def gather_rows(q, d_out, plan, lists, lse, delta):
     """List-ordered copies of q / d_out rows and of their lse / delta: (qg, dog [R*H,128], lse_g, delta_g [R*H])."""
     S, H, D = q.shape
-    list_off, work_off, list_tok = lists
+    list_off, work_off, list_tok, tile_rec = _split_lists(lists)
     R = max(plan.rows_total(H), 1)
     qg = torch.empty((R, D), dtype=q.dtype, device=q.device)
     dog = torch.empty((R, D), dtype=q.dtype, device=q.device)
@@ -315,8 +335,8 @@ def gather_rows(q, d_out, plan, lists, lse, delta):
     if plan.kk > 0:
         with _timed("gather_rows", q.device):
             call("moba_gather_rows", _ptr(q), _ptr(d_out), _ptr(lse), _ptr(delta), _DTYPES[q.dtype], H, q.stride(0),
-                 q.stride(1), ctypes.byref(plan.info), _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(qg),
-                 _ptr(dog), _ptr(lse_g), _ptr(delta_g), _dev_index(q), _stream(q.device))
+                 q.stride(1), ctypes.byref(plan.info), _ptr(list_off), _ptr(work_off), _ptr(list_tok), _ptr(tile_rec),
+                 _ptr(qg), _ptr(dog), _ptr(lse_g), _ptr(delta_g), _dev_index(q), _stream(q.device))
     return qg, dog, lse_g, delta_g
 
 
@@ -353,7 +373,7 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
     leaving the choice to the chunk size."""
     S, H, D = q.shape
     kv = _kv_layout(q, k, v)
-    list_off, work_off, list_tok = lists
+    list_off, work_off, list_tok, tile_rec = _split_lists(lists)
     if gathered is None:
         gathered = gather_rows(q, d_out, plan, lists, lse, delta) if (parts & 2 and plan.kk > 0) else (None,) * 4
     qg, dog, lse_g, delta_g = gathered
@@ -362,7 +382,8 @@ def attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status, parts=3, gather
     with _timed("attn_bwd_dq", q.device):
         call("moba_attn_bwd_dq", _ptr(q), _ptr(k), _ptr(v), _ptr(d_out), _DTYPES[q.dtype], H, q.stride(0),
              q.stride(1), kv, ctypes.byref(plan.info), _ptr(plan.meta), _ptr(list_off), _ptr(work_off), _ptr(list_tok),
-             _ptr(qg), _ptr(dog), _ptr(lse_g), _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dq_self), _ptr(part_dq),
+             _ptr(tile_rec), _ptr(qg), _ptr(dog), _ptr(lse_g), _ptr(delta_g), _ptr(lse), _ptr(delta), _ptr(dq_self),
+             _ptr(part_dq),
              parts | _DQ_FORMS[form], float(scale), _ptr(status), _dev_index(q), _stream(q.device))
     return dq_self, part_dq
 
