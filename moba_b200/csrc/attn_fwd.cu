@@ -284,7 +284,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
       // in use (two sub-passes of 32 columns to bound the registers).
       uint32_t pk[32];
       float mx = -INFINITY, ls0 = 0.f, ls1 = 0.f;
-      auto probabilities = [&](bool with_max) {
+      auto probabilities = [&](const bool with_max, const bool with_exp) {
         ls0 = 0.f;
         ls1 = 0.f;
 #pragma unroll
@@ -297,29 +297,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
             for (int c = 0; c < 16; ++c) {
               const float s0 = __uint_as_float(s[2 * c]), s1 = __uint_as_float(s[2 * c + 1]);
               if (with_max) mx = fmaxf(mx, fmaxf(s0, s1));
-              const float p0 = ex2_approx(fmaf(s0, sc, -m_used));
-              const float p1 = ex2_approx(fmaf(s1, sc, -m_used));
-              ls0 += p0;
-              ls1 += p1;
-              pk[h * 16 + c] = pack2<kBf16>(p0, p1);
+              if (with_exp) {
+                const float p0 = ex2_approx(fmaf(s0, sc, -m_used));
+                const float p1 = ex2_approx(fmaf(s1, sc, -m_used));
+                ls0 += p0;
+                ls1 += p1;
+                pk[h * 16 + c] = pack2<kBf16>(p0, p1);
+              }
             }
           } else {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const float s0 = __uint_as_float(s[2 * c]), s1 = __uint_as_float(s[2 * c + 1]);
-              float p0 = ex2_approx(fmaf(s0, sc, -m_used));
-              float p1 = ex2_approx(fmaf(s1, sc, -m_used));
               const int c0 = h * 32 + 2 * c;
-              if (c0 < ncol) { if (with_max) mx = fmaxf(mx, s0); } else p0 = 0.f;
-              if (c0 + 1 < ncol) { if (with_max) mx = fmaxf(mx, s1); } else p1 = 0.f;
-              ls0 += p0;
-              ls1 += p1;
-              pk[h * 16 + c] = pack2<kBf16>(p0, p1);
+              if (with_max) {
+                if (c0 < ncol) mx = fmaxf(mx, s0);
+                if (c0 + 1 < ncol) mx = fmaxf(mx, s1);
+              }
+              if (with_exp) {
+                float p0 = ex2_approx(fmaf(s0, sc, -m_used));
+                float p1 = ex2_approx(fmaf(s1, sc, -m_used));
+                if (c0 >= ncol) p0 = 0.f;
+                if (c0 + 1 >= ncol) p1 = 0.f;
+                ls0 += p0;
+                ls1 += p1;
+                pk[h * 16 + c] = pack2<kBf16>(p0, p1);
+              }
             }
           }
         }
       };
-      probabilities(true);
+      // The first key tile has no maximum in use yet: only the row maximum is taken in the first pass (the
+      // probabilities follow below, once, against it). Later tiles compute them in the same pass, speculatively.
+      if (j == 0) probabilities(true, false);
+      else probabilities(true, true);
       sm.xchg[ch][row] = mx;
       // also orders the in-place write of P below after every S load of the row's two threads
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
@@ -349,7 +360,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
           }
         }
         m_used = m_new;
-        probabilities(false);      // S is still intact: P has not been written yet
+        probabilities(false, true);      // S is still intact: P has not been written yet
         // the partner may already write P over columns this thread has just read again
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       }
