@@ -94,24 +94,6 @@ __device__ __forceinline__ TileItem lookup_tile(const Args& a, int w, int lane, 
   return it;
 }
 
-// `nthreads` (a multiple of 16, at most 128) threads copy 128 rows x 256 B (row i from token row_tok[i], head
-// `head`) into two swizzled [128 x 64] sub-tiles at dst / dst + 16384; rows with a negative token are
-// zero-filled. `t` is the thread's index inside the copying group.
-__device__ __forceinline__ void gather_rows(uint8_t* dst, const uint16_t* src, const int* row_tok, int head,
-                                            int64_t stride_s, int64_t stride_h, int t, int nthreads = 128) {
-  const int rows_per_pass = nthreads >> 4;
-  for (int row = t >> 4; row < 128; row += rows_per_pass) {
-    const int c16 = t & 15;
-    const int tok = row_tok[row];
-    const uint32_t d = smem_u32(dst) + (c16 >> 3) * 16384u + sw128_offset(row, c16 & 7);
-    if (tok >= 0) {
-      cp_async16(d, src + static_cast<int64_t>(tok) * stride_s + static_cast<int64_t>(head) * stride_h + c16 * 8);
-    } else {
-      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(d), "r"(0u) : "memory");
-    }
-  }
-}
-
 // Four 32-byte pieces per lane (r[8 p .. 8 p + 7] = piece p of the lane's row) are swapped inside each quad of
 // lanes, so that afterwards lane a holds piece a of the quad's row i in slot i: a store of slot i then writes whole
 // 128-byte lines (four lanes x 32 bytes of one row) instead of 32 bytes to each of 32 lines.

@@ -52,7 +52,6 @@ struct __align__(1024) FwdSmem {
   uint32_t tmem_base;
   int abort_flag;
   int work[8];           // chunk, head, first row / token, n_rows, nkv, key token start, keys in chunk, active
-  int row_tok[128];
 };
 
 struct FwdArgs {
@@ -174,11 +173,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
   const int head_kv = head / a.kv_rep;               // key/value head of this query head
   const int row = tid & 127, ch = (warp >> 2) & 1;   // query row of a softmax thread; its 64-column half
 
-  if (warp < 4) {
-    int tok = -1;
-    if (row < n_rows) tok = kGathered ? a.list_tok[first + row] : first + row;
-    sm.row_tok[row] = tok;
-  } else if (warp == kTmaWarp && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     // the first K and V tiles travel while the Q rows are gathered
     mbar_arrive_expect_tx(&sm.bar_k_full, 32768);
     tma_load_3d(smem_u32(sm.k[0]), &map_k, &sm.bar_k_full, 0, head_kv, key0);
@@ -187,11 +182,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     tma_load_3d(smem_u32(sm.v[0]), &map_v, &sm.bar_v_full, 0, head_kv, key0);
     tma_load_3d(smem_u32(sm.v[1]), &map_v, &sm.bar_v_full, 64, head_kv, key0);
   }
-  __syncthreads();
 
-  // ---- Q tile: rows gathered by token index into the swizzled K-major layout (256 threads) -----------
+  // ---- Q tile: rows gathered by token index into the swizzled K-major layout (256 threads: 16 per row, eight rows
+  // each; a thread reads the tokens of its eight rows itself, all eight loads in flight together) -----------
   if (warp < 8) {
-    gather_rows(sm.q[0], a.q, sm.row_tok, head, a.stride_s, a.stride_h, tid, 256);
+    const int c16 = tid & 15, r0 = tid >> 4;
+    int toks[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = r0 + 16 * i;
+      toks[i] = r < n_rows ? (kGathered ? __ldg(&a.list_tok[first + r]) : first + r) : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = r0 + 16 * i;
+      const uint32_t d = smem_u32(sm.q[0]) + (c16 >> 3) * 16384u + sw128_offset(r, c16 & 7);
+      if (toks[i] >= 0) {
+        cp_async16(d, a.q + static_cast<int64_t>(toks[i]) * a.stride_s + static_cast<int64_t>(head) * a.stride_h + c16 * 8);
+      } else {
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(d), "r"(0u) : "memory");   // rows past the tile's end
+      }
+    }
     cp_async_wait_all();
     fence_proxy_async_smem();
   }
