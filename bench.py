@@ -641,13 +641,13 @@ def run_decode(args, cfg_id, cfg):
 
 
 def launches_per_step(cfg, world):
-    """Kernels of libmoba_b200.so launched per step: pool 2, gate 1, lists 3, forward tiles 2, merge 1, and in
-    backward delta 1, row gather 1, dK/dV 1, dQ 2, dq merge 1. A forward-only run on several GPUs works in two
-    head groups (twice the forward launches)."""
+    """Kernels of libmoba_b200.so launched per step: pool 2, gate 1, lists 4 (scan, offsets, fill, tile records),
+    forward tiles 2, merge 1, and in backward delta 1, row gather 1, dK/dV 1, dQ 2, dq merge 1. A forward-only run on
+    several GPUs works in two head groups (twice the forward launches)."""
     hl = cfg["heads"] // world
     if world > 1 and not cfg["backward"] and hl >= 2:
-        return 18
-    return 9 + (6 if cfg["backward"] else 0)
+        return 20
+    return 10 + (6 if cfg["backward"] else 0)
 
 
 def main():
