@@ -188,7 +188,7 @@ merge_dq_kernel(uint16_t* __restrict__ dq, const float* __restrict__ dq_self, in
 }
 
 // Copies the rows every (chunk, head) list names into list order: qg / dog [R*H, 128] and lse_g / delta_g
-// [R*H]. One CTA per 128-row list tile (found by binary search in work_off, like the attention kernels); a
+// [R*H]. One CTA per 128-row list tile (its record from moba_tile_records, else a binary search in work_off); a
 // warp moves one row per step, 8 bytes per lane and tensor. The dK/dV kernel re-reads every list 128-key-tile
 // many times, so it takes contiguous tiles by TMA instead of gathering rows itself.
 __global__ void __launch_bounds__(256)
