@@ -452,6 +452,7 @@ def run_ours(args, cfg_id, cfg):
         s1.record()
         barrier()
         te = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
+        own_ms = float(te.item()) / e2e_steps
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = float(te.item()) / e2e_steps
@@ -464,6 +465,15 @@ def run_ours(args, cfg_id, cfg):
 
             e2e["copy_rates"] = {"head_slices": copy_stats["slices"], "h2d_gbs_per_slice": rate("h2d"),
                                  "d2h_gbs_per_slice": rate("d2h"), "host_numa_node": numa_node}
+        if world > 1:
+            # every rank's own end-to-end time and slowest slice copies: the ranks share the host's memory system
+            mine = {"ms": round(own_ms, 2)}
+            if copy_stats:
+                mine["h2d_min_gbs"] = min((x for x in e2e["copy_rates"]["h2d_gbs_per_slice"] if x), default=None)
+                mine["d2h_min_gbs"] = min((x for x in e2e["copy_rates"]["d2h_gbs_per_slice"] if x), default=None)
+            per_rank = [None] * world
+            dist.all_gather_object(per_rank, mine)
+            e2e["per_rank"] = per_rank
     check_kernel_status(dev)
 
     # ---- checksums (outside every timed region): equal bits at every N ---------------------------------
@@ -539,6 +549,8 @@ def run_ours(args, cfg_id, cfg):
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
             if "copy_rates" in e2e:
                 line["e2e"]["copy_rates_rank0"] = e2e["copy_rates"]
+            if "per_rank" in e2e:
+                line["e2e"]["per_rank"] = e2e["per_rank"]
         emit(line)
     if world > 1:
         dist.destroy_process_group()

@@ -384,3 +384,47 @@ def test_dq_kernel_forms_give_the_same_bits(cuda_device, chunk, topk):
     assert torch.equal(got["tile"][0], got["persistent"][0])
     assert torch.equal(got["tile"][1], got["persistent"][1])
     assert got["tile"][0].abs().max().item() > 0
+
+
+def test_tile_records_equal_the_offset_search(cuda_device):
+    """The list kernels find a work tile's list either from its record (moba_tile_records) or by searching the work
+    offsets: forward partials, list-ordered copies and dq partials are the same bits either way."""
+    from moba_b200 import ops
+
+    dev = cuda_device
+    lens = [3000, 129, 9000, 64, 16384]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    S, H, chunk, topk = cu[-1], 3, 1024, 4
+    g = torch.Generator(device=dev).manual_seed(5)
+    q, k, v, d_out = (torch.randn(S, H, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(4))
+    plan = ops.get_plan(cu, chunk, topk, dev)
+    status = ops.new_status(dev)
+    sel, _, tile_cnt = ops.gate_topk(q, ops.pool_keys(k, plan), plan, status=status)
+    list_off, work_off, list_tok, row_of = ops.build_lists(plan, H, sel, tile_cnt, status=status)
+    rec = ops.tile_records(plan, H, list_off, work_off)
+    # the records against the tables they come from
+    wo, lo = work_off.cpu().numpy(), list_off.cpu().numpy()
+    r = rec.cpu().numpy()
+    n_tiles = int(wo[-1])
+    assert (r[n_tiles:, 2] == 0).all() and (r[:n_tiles, 2] > 0).all()
+    e = np.searchsorted(wo, np.arange(n_tiles), side="right") - 1
+    assert (r[:n_tiles, 0] == e % H).all()
+    assert (r[:n_tiles, 1] == lo[e] + (np.arange(n_tiles) - wo[e]) * 128).all()
+    assert (r[:n_tiles, 2] == np.minimum(128, lo[e + 1] - r[:n_tiles, 1])).all()
+    n = plan.rows_total(H)
+    res = {}
+    for name, lists in (("search", (list_off, work_off, list_tok)), ("records", (list_off, work_off, list_tok, rec))):
+        out, lse, part_o, part_lse = ops.attn_fwd(q, k, v, plan, lists, status)
+        out2, lse2 = out.clone(), lse.clone()
+        ops.merge_fwd(out2, lse2, plan, part_o, part_lse, row_of)
+        delta = ops.bwd_delta(out2, d_out)
+        gathered = ops.gather_rows(q, d_out, plan, lists, lse2, delta)
+        dqs = [ops.attn_bwd_dq(q, k, v, d_out, plan, lists, lse2, delta, status, gathered=gathered, form=f)
+               for f in ("tile", "persistent")]
+        res[name] = [part_o[:n], part_lse[:n], gathered[0][:n], gathered[1][:n], gathered[2][:n], gathered[3][:n]] + \
+                    [t for dq_self, part_dq in dqs for t in (dq_self, part_dq[:n])]
+    ops.check_status(status)
+    for a_, b_ in zip(res["search"], res["records"]):
+        assert torch.equal(a_, b_)
