@@ -428,3 +428,65 @@ def test_tile_records_equal_the_offset_search(cuda_device):
     ops.check_status(status)
     for a_, b_ in zip(res["search"], res["records"]):
         assert torch.equal(a_, b_)
+
+
+def test_random_shapes_kernel_forms_and_lookups_agree(cuda_device):
+    """Seeded random ragged batches (chunk 64..4096, one to six sequences with lengths off every tile boundary,
+    grouped-query K / V, both 16-bit types): the record and search lookups and the two dQ kernel forms give the same
+    bits for every tensor of the forward and the backward, and all of them are finite."""
+    import random
+
+    from moba_b200 import ops
+
+    dev = cuda_device
+    rnd = random.Random(1234)
+    n_checked = 0
+    for it in range(60):
+        nseq = rnd.randint(1, 6)
+        chunk = rnd.choice([64, 96, 128, 192, 256, 512, 1024, 2048, 4096])
+        topk = rnd.randint(2, 6)
+        lens = [rnd.randint(1, 6 * chunk + 300) for _ in range(nseq)]
+        if rnd.random() < 0.2:
+            lens[rnd.randrange(nseq)] = rnd.randint(1, 40)
+        hkv, rep = rnd.choice([1, 1, 2, 3]), rnd.choice([1, 1, 2, 4])
+        Hq = hkv * rep
+        dt = rnd.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        S = cu[-1]
+        g = torch.Generator(device=dev).manual_seed(it)
+        q, d_out = (torch.randn(S, Hq, 128, generator=g, device=dev).to(dt) for _ in range(2))
+        k, v = (torch.randn(S, hkv, 128, generator=g, device=dev).to(dt) for _ in range(2))
+        plan = ops.get_plan(cu, chunk, topk, dev)
+        if plan.kk == 0:
+            continue
+        status = ops.new_status(dev)
+        sel, _, tile_cnt = ops.gate_topk(q, ops.pool_keys(k, plan), plan, status=status)
+        list_off, work_off, list_tok, row_of = ops.build_lists(plan, Hq, sel, tile_cnt, status=status)
+        rec = ops.tile_records(plan, Hq, list_off, work_off)
+        n = plan.rows_total(Hq)
+        res = {}
+        for name, lists in (("search", (list_off, work_off, list_tok)),
+                            ("records", (list_off, work_off, list_tok, rec))):
+            out, lse, part_o, part_lse = ops.attn_fwd(q, k, v, plan, lists, status)
+            ops.merge_fwd(out, lse, plan, part_o, part_lse, row_of)
+            delta = ops.bwd_delta(out, d_out)
+            gathered = ops.gather_rows(q, d_out, plan, lists, lse, delta)
+            dk, dv = ops.attn_bwd_dkdv(q, k, v, d_out, plan, lists, lse, delta, status, gathered=gathered)
+            tensors = [out, lse, part_o[:n], part_lse[:n], dk, dv] + [t[:n] for t in gathered]
+            for form in ("tile", "persistent"):
+                dq_self, part_dq = ops.attn_bwd_dq(q, k, v, d_out, plan, lists, lse, delta, status,
+                                                   gathered=gathered, form=form)
+                tensors += [dq_self, part_dq[:n]]
+            res[name] = tensors
+        ops.check_status(status)
+        tag = f"case {it}: lens={lens} chunk={chunk} topk={topk} H={Hq}/{hkv} {dt}"
+        for i, (a_, b_) in enumerate(zip(res["search"], res["records"])):
+            assert torch.equal(a_, b_), f"{tag}: tensor {i} differs between the lookups"
+        a_ = res["search"]
+        assert torch.equal(a_[-4], a_[-2]) and torch.equal(a_[-3], a_[-1]), f"{tag}: dQ forms differ"
+        for i in (0, 4, 5, -2, -1):
+            assert torch.isfinite(a_[i].float()).all().item(), f"{tag}: tensor {i} is not finite"
+        n_checked += 1
+    assert n_checked >= 50
