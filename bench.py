@@ -431,6 +431,9 @@ def run_ours(args, cfg_id, cfg):
         out_dev = torch.empty((S, hl, D), dtype=torch.bfloat16, device=dev) if world > 1 else None
 
         copy_stats = {}
+        # eight ranks copying in both directions at once slow each other down on the host side (measured: a slice
+        # copy takes 3-5x longer while the other direction is busy); one direction at a time is faster there
+        duplex = args.copy_order == "duplex" or (args.copy_order == "auto" and world < 8)
 
         def e2e_step(stats=None):
             # host tensors in, host tensors out, through the package's host entry point: head groups are
@@ -438,7 +441,7 @@ def run_ours(args, cfg_id, cfg):
             moba_attn_varlen_host(hq, hk, hv, cu, max(cfg["lens"]), cfg["chunk"], cfg["topk"],
                                   d_out=hdo if cfg["backward"] else None, out=ho,
                                   grads=tuple(hgrads) if cfg["backward"] else None, head_groups=args.head_groups,
-                                  device=dev, out_device=out_dev, stats=stats)
+                                  device=dev, out_device=out_dev, stats=stats, duplex=duplex)
             if world > 1:
                 dist.all_gather_into_tensor(out_all, out_dev)
 
@@ -456,6 +459,10 @@ def run_ours(args, cfg_id, cfg):
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = float(te.item()) / e2e_steps
+        steady = {}
+        if world > 1:
+            e2e_step(steady)          # one more untimed call: the device timeline of a step in steady state
+            barrier()
         nbytes = hq.numel() * 2
         e2e = dict(ms=e2e_ms, h2d=4 * nbytes if cfg["backward"] else 3 * nbytes,
                    d2h=(4 if cfg["backward"] else 1) * nbytes)
@@ -471,6 +478,11 @@ def run_ours(args, cfg_id, cfg):
             if copy_stats:
                 mine["h2d_min_gbs"] = min((x for x in e2e["copy_rates"]["h2d_gbs_per_slice"] if x), default=None)
                 mine["d2h_min_gbs"] = min((x for x in e2e["copy_rates"]["d2h_gbs_per_slice"] if x), default=None)
+            if steady:
+                # [copy-in begin, end, kernels begin, end, copy-out begin, end] per head slice, ms from the call
+                mine["timeline_ms"] = steady["timeline"]
+                mine["host_issue_ms"] = round(steady["host_issue_ms"], 2)
+            mine["copy_order"] = "duplex" if duplex else "in-first"
             per_rank = [None] * world
             dist.all_gather_object(per_rank, mine)
             e2e["per_rank"] = per_rank
@@ -671,6 +683,9 @@ def main():
     ap.add_argument("--config", type=int, default=3, choices=sorted(CONFIGS))
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--head-groups", type=int, default=8, help="head slices pipelined in the end-to-end leg")
+    ap.add_argument("--copy-order", choices=["auto", "duplex", "in-first"], default="auto",
+                    help="end-to-end leg: host<->device copies in both directions at once (duplex) or all copy-ins "
+                         "before the copy-outs (in-first); auto = in-first from 8 ranks per host up")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-numa-bind", action="store_true", help="leave the process's CPU affinity alone")
     ap.add_argument("--no-secondary", action="store_true", help="skip the 1M-token forward-only line (config 3 runs)")

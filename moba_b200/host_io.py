@@ -9,6 +9,8 @@ behind the compute; issued back to back on one stream they add 40 % to a step.
 `moba_attn_varlen_host` is the same operator as `moba_attn_varlen` (same argument meaning) with host tensors in
 and host tensors out; it also peaks at 1 / head_groups of the device memory for intermediates.
 """
+import time
+
 import torch
 
 from . import ops
@@ -51,7 +53,7 @@ def bind_host_to_device_numa(device):
 
 
 def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, d_out=None, out=None,
-                          grads=None, head_groups=4, device=None, out_device=None, stats=None):
+                          grads=None, head_groups=4, device=None, out_device=None, stats=None, duplex=True):
     """MoBA attention (and, with d_out, its backward) on pinned host tensors [seqlen, head, head_dim].
 
     Args:
@@ -62,10 +64,17 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
         grads: (dq, dk, dv) pinned host tensors to receive the gradients (allocated when None and d_out is given)
         head_groups: number of head slices in flight one after the other (clamped to the key/value head count);
             with more than one, the first and the last slice are additionally cut down to one key/value head
+        duplex: True -- two staging sets, copy-in of slice g + 1 and copy-out of slice g - 1 run beside the kernels of
+            slice g on two copy streams (both directions of the link at once). False -- every slice has its own
+            staging set, all copy-ins are queued first and the copy-outs follow them on the same stream, so the link
+            carries one direction at a time: for hosts on which many GPUs copy at once and simultaneous reads and
+            writes of host memory slow each other down (measured with eight ranks on one host)
         out_device: optional device tensor [seqlen, head, head_dim] that also receives the output (e.g. to feed
             a collective); written on the current stream
         stats: optional dict; receives "h2d" and "d2h", lists of (bytes, milliseconds) per head slice measured with
-            events on the two copy streams (the achieved copy rates of the slices)
+            events on the two copy streams (the achieved copy rates of the slices), "timeline" (per slice, milliseconds
+            from the start of the call at which its copy-in, kernels and copy-out begin and end on the device) and
+            "host_issue_ms" (host time until everything was enqueued)
     Returns:
         out, or (out, (dq, dk, dv)) when d_out is given. The results are complete when this function returns.
     """
@@ -97,29 +106,36 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
     bounds = [b * rep for b in kv_bounds]
 
     compute = torch.cuda.current_stream(device)
-    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    s_in = torch.cuda.Stream(device)
+    s_out = torch.cuda.Stream(device) if duplex else s_in
     s_in.wait_stream(compute)
-    # two sets of input staging buffers: group g + 1 is copied in while group g computes
+    # input staging buffers: two sets (group g + 1 is copied in while group g computes), or one per group
+    n_sets = 2 if duplex else groups
     width = max(b - a for a, b in zip(bounds, bounds[1:]))
     srcs = (q, k, v, d_out) if backward else (q, k, v)
     is_kv = (False, True, True, False)
     stage = [[torch.empty((S, width // rep if kv else width, D), dtype=q.dtype, device=device)
-              for kv in is_kv[:len(srcs)]] for _ in range(2)]
+              for kv in is_kv[:len(srcs)]] for _ in range(n_sets)]
     ev_in = [torch.cuda.Event() for _ in range(groups)]
     ev_done = [torch.cuda.Event() for _ in range(groups)]
     timed = stats is not None
     t_in = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)] if timed else None
     t_out = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)] if timed else None
+    t_run = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)] if timed else None
+    if timed:
+        t_base = torch.cuda.Event(enable_timing=True)
+        t_base.record(compute)
+        host_t0 = time.perf_counter()
     n_in = [0] * groups
     n_out = [0] * groups
 
     def copy_in(g):
         with torch.cuda.stream(s_in):
-            if g >= 2:
-                s_in.wait_event(ev_done[g - 2])          # the staging set is free again
+            if g >= n_sets:
+                s_in.wait_event(ev_done[g - n_sets])     # the staging set is free again
             if timed:
                 t_in[g][0].record(s_in)
-            for dst, src, kv in zip(stage[g % 2], srcs, is_kv):
+            for dst, src, kv in zip(stage[g % n_sets], srcs, is_kv):
                 h0, h1 = (kv_bounds[g], kv_bounds[g + 1]) if kv else (bounds[g], bounds[g + 1])
                 ops.copy_heads(dst[:, : h1 - h0], src[:, h0:h1], s_in)
                 n_in[g] += S * (h1 - h0) * D * src.element_size()
@@ -127,14 +143,17 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
                 t_in[g][1].record(s_in)
             ev_in[g].record(s_in)
 
-    copy_in(0)
+    for g in range(1 if duplex else groups):
+        copy_in(g)
     for g in range(groups):
-        if g + 1 < groups:
+        if duplex and g + 1 < groups:
             copy_in(g + 1)
         h0, h1 = bounds[g], bounds[g + 1]
         k0, k1 = kv_bounds[g], kv_bounds[g + 1]
         compute.wait_event(ev_in[g])
-        ins = [t[:, : (k1 - k0) if kv else (h1 - h0)] for t, kv in zip(stage[g % 2], is_kv)]
+        if timed:
+            t_run[g][0].record(compute)
+        ins = [t[:, : (k1 - k0) if kv else (h1 - h0)] for t, kv in zip(stage[g % n_sets], is_kv)]
         if backward:
             tq, tk, tv = (t.detach().requires_grad_() for t in ins[:3])
             o = moba_attn_varlen(tq, tk, tv, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk)
@@ -147,6 +166,8 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
             results = [(out, o, h0, h1)]
         if out_device is not None:
             out_device[:, h0:h1].copy_(results[0][1])
+        if timed:
+            t_run[g][1].record(compute)
         ev_done[g].record(compute)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[g])
@@ -160,10 +181,14 @@ def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba
                 t_out[g][1].record(s_out)
     compute.wait_stream(s_out)
     compute.wait_stream(s_in)
-    for buf in stage[0] + stage[1]:
+    for buf in (b for bufs in stage for b in bufs):
         buf.record_stream(s_in)
+    if timed:
+        stats["host_issue_ms"] = (time.perf_counter() - host_t0) * 1e3
     torch.cuda.current_stream(device).synchronize()
     if timed:
+        stats["timeline"] = [[round(t_base.elapsed_time(e), 2) for pair in (t_in[g], t_run[g], t_out[g]) for e in pair]
+                             for g in range(groups)]
         stats["h2d"] = [(n_in[g], t_in[g][0].elapsed_time(t_in[g][1])) for g in range(groups)]
         stats["d2h"] = [(n_out[g], t_out[g][0].elapsed_time(t_out[g][1])) for g in range(groups)]
         stats["slices"] = [b - a for a, b in zip(bounds, bounds[1:])]

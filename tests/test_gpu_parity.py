@@ -254,10 +254,12 @@ def test_bitwise_run_to_run_determinism(cuda_device):
 
 
 
+@pytest.mark.parametrize("duplex", [True, False])
 @pytest.mark.parametrize("groups", [1, 3, 8])
-def test_host_entry_point_matches_device_call(cuda_device, groups):
-    """moba_attn_varlen_host (pinned host tensors, head groups pipelined over copy and compute streams) returns
-    bit for bit what moba_attn_varlen returns on device tensors: heads are independent."""
+def test_host_entry_point_matches_device_call(cuda_device, groups, duplex):
+    """moba_attn_varlen_host (pinned host tensors, head groups pipelined over copy and compute streams, with both
+    copy directions at once or one at a time) returns bit for bit what moba_attn_varlen returns on device tensors:
+    heads are independent."""
     from moba_b200 import moba_attn_varlen_host
 
     q, k, v, d_out = H.make_inputs(51, 1536, 6)
@@ -265,11 +267,16 @@ def test_host_entry_point_matches_device_call(cuda_device, groups):
     want = run_api(q, k, v, d_out, cu, 128, 3, cuda_device)
     hq, hk, hv, hdo = (torch.from_numpy(x).to(torch.bfloat16).pin_memory() for x in (q, k, v, d_out))
     cu_t = torch.tensor(cu, dtype=torch.int32, device=cuda_device)
+    stats = {}
     out, grads = moba_attn_varlen_host(hq, hk, hv, cu_t, 1036, 128, 3, d_out=hdo, head_groups=groups,
-                                       device=cuda_device)
+                                       device=cuda_device, duplex=duplex, stats=stats)
     for name, g, w in zip(("out", "dq", "dk", "dv"), (out,) + tuple(grads), want):
         assert np.array_equal(g.float().numpy(), w), name
-    fwd_only = moba_attn_varlen_host(hq, hk, hv, cu_t, 1036, 128, 3, head_groups=groups, device=cuda_device)
+    assert sum(stats["slices"]) == 6 and len(stats["timeline"]) == len(stats["slices"])
+    if not duplex:      # every copy-in ends before the first copy-out begins
+        assert max(t[1] for t in stats["timeline"]) <= min(t[4] for t in stats["timeline"]) + 1e-3
+    fwd_only = moba_attn_varlen_host(hq, hk, hv, cu_t, 1036, 128, 3, head_groups=groups, device=cuda_device,
+                                     duplex=duplex)
     assert np.array_equal(fwd_only.float().numpy(), want[0])
 
 
