@@ -334,7 +334,7 @@ def run_ours(args, cfg_id, cfg):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     # the pinned host buffers of the end-to-end leg should sit on the GPU's NUMA node (one process per GPU)
-    from moba_b200.host_io import bind_host_to_device_numa
+    from moba_b200.host_io import bind_host_to_device_numa, host_numa_nodes
 
     numa_node = None if args.no_numa_bind else bind_host_to_device_numa(dev)
     if world > 1:
@@ -471,7 +471,8 @@ def run_ours(args, cfg_id, cfg):
                 return [round(b / ms / 1e6, 1) if ms > 0 else None for b, ms in copy_stats[key]]
 
             e2e["copy_rates"] = {"head_slices": copy_stats["slices"], "h2d_gbs_per_slice": rate("h2d"),
-                                 "d2h_gbs_per_slice": rate("d2h"), "host_numa_node": numa_node}
+                                 "d2h_gbs_per_slice": rate("d2h"), "host_numa_node": numa_node,
+                                 "host_numa_nodes": {str(n): len(c) for n, c in sorted(host_numa_nodes().items())}}
         if world > 1:
             # every rank's own end-to-end time and slowest slice copies: the ranks share the host's memory system
             mine = {"ms": round(own_ms, 2)}
@@ -483,6 +484,7 @@ def run_ours(args, cfg_id, cfg):
                 mine["timeline_ms"] = steady["timeline"]
                 mine["host_issue_ms"] = round(steady["host_issue_ms"], 2)
             mine["copy_order"] = "duplex" if duplex else "in-first"
+            mine["numa_node"] = numa_node
             per_rank = [None] * world
             dist.all_gather_object(per_rank, mine)
             e2e["per_rank"] = per_rank

@@ -52,6 +52,27 @@ def bind_host_to_device_numa(device):
         return None
 
 
+def host_numa_nodes():
+    """{node: set of CPUs} for the NUMA nodes of this host that have CPUs (from sysfs); empty if unreadable."""
+    import glob
+    import os
+
+    nodes = {}
+    try:
+        for path in glob.glob("/sys/devices/system/node/node[0-9]*"):
+            with open(os.path.join(path, "cpulist")) as f:
+                text = f.read().strip()
+            cpus = set()
+            for part in text.split(",") if text else []:
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+            if cpus:
+                nodes[int(os.path.basename(path)[4:])] = cpus
+    except (OSError, ValueError):
+        return {}
+    return nodes
+
+
 def moba_attn_varlen_host(q, k, v, cu_seqlens, max_seqlen, moba_chunk_size, moba_topk, d_out=None, out=None,
                           grads=None, head_groups=4, device=None, out_device=None, stats=None, duplex=True):
     """MoBA attention (and, with d_out, its backward) on pinned host tensors [seqlen, head, head_dim].
