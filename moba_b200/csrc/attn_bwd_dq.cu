@@ -405,16 +405,6 @@ struct __align__(1024) DqPersistSmem {
   int abort_flag;
 };
 
-// 32 consecutive fp32 values of one row -> global memory as four 32-byte stores
-__device__ __forceinline__ void store_row_slice_f32(float* dst, const uint32_t (&r)[32]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 8 * i), "r"(r[8 * i]),
-                 "r"(r[8 * i + 1]), "r"(r[8 * i + 2]), "r"(r[8 * i + 3]), "r"(r[8 * i + 4]), "r"(r[8 * i + 5]),
-                 "r"(r[8 * i + 6]), "r"(r[8 * i + 7])
-                 : "memory");
-}
-
 template <bool kBf16, bool kGathered>
 __global__ void __launch_bounds__(kDqThreads, 1)
 attn_bwd_dq_persist_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,

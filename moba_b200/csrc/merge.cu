@@ -124,6 +124,81 @@ merge_fwd_kernel(uint16_t* __restrict__ out, float* __restrict__ lse, int64_t n_
   }
 }
 
+// merge_fwd for rows with at most two partials (kk <= 2): a warp takes two rows per iteration, one per half warp
+// for the row_of / log-sum-exp part, so that six row loads are in flight instead of three. The arithmetic per row
+// is that of merge_fwd_kernel in the same order (the sums have at most two non-zero terms), so the bits are the same.
+template <bool kBf16>
+__global__ void __launch_bounds__(kRowWarps * 32)
+merge_fwd_pair_kernel(uint16_t* __restrict__ out, float* __restrict__ lse, int64_t n_rows, int kk,
+                      const uint16_t* __restrict__ part_o, const float* __restrict__ part_lse,
+                      const int32_t* __restrict__ row_of) {
+  const int lane = threadIdx.x & 31, half = lane >> 4, slot = lane & 15;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kRowWarps * 2;
+  int64_t base = (static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5)) * 2;
+  if (base >= n_rows) return;
+  auto slot_row = [&](int64_t b) {          // lanes 0.. of each half: the partial rows of row b + half
+    const int64_t row = b + half;
+    return (slot < kk && row < n_rows) ? __ldg(row_of + row * kk + slot) : -1;
+  };
+  int r_next = slot_row(base);
+  for (; base < n_rows; base += step) {
+    const int r = r_next;
+    if (base + step < n_rows) r_next = slot_row(base + step);
+    const float lj = r >= 0 ? __ldg(part_lse + r) : -INFINITY;
+    uint2 bits[2][2], self_bits[2];
+    float ls[2];
+    uint2* orow[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const bool live = base + x < n_rows;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int rj = __shfl_sync(0xffffffffu, r, 16 * x + j);
+        bits[x][j] = (j < kk && rj >= 0)
+                         ? __ldg(reinterpret_cast<const uint2*>(part_o + static_cast<int64_t>(rj) * MOBA_HEAD_DIM) + lane)
+                         : make_uint2(0u, 0u);
+      }
+      orow[x] = reinterpret_cast<uint2*>(out + (base + (live ? x : 0)) * MOBA_HEAD_DIM) + lane;
+      self_bits[x] = *orow[x];
+      ls[x] = lse[base + (live ? x : 0)];
+    }
+    // per half warp: m and se of its row
+    const float ls_mine = half ? ls[1] : ls[0];
+    float m = fmaxf(ls_mine, lj);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float wj = (r >= 0) ? __expf(lj - m) : 0.f;
+    const float ws_mine = __expf(ls_mine - m);
+    float se = wj;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+    se += ws_mine;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const float m_x = __shfl_sync(0xffffffffu, m, 16 * x), se_x = __shfl_sync(0xffffffffu, se, 16 * x);
+      const float ws = __shfl_sync(0xffffffffu, ws_mine, 16 * x);
+      const float inv = 1.0f / se_x;
+      float acc[4], f[4];
+      unpack4<kBf16>(self_bits[x], f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = f[i] * ws;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float w = __shfl_sync(0xffffffffu, wj, 16 * x + j);
+        unpack4<kBf16>(bits[x][j], f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf(f[i], (j < kk) ? w : 0.f, acc[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] *= inv;
+      if (base + x < n_rows) {
+        *orow[x] = pack4<kBf16>(acc);
+        if (lane == 0) lse[base + x] = m_x + __logf(se_x);
+      }
+    }
+  }
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kRowWarps * 32)
 delta_kernel(const uint16_t* __restrict__ out, const uint16_t* __restrict__ d_out, int64_t n_rows,
@@ -266,7 +341,11 @@ extern "C" int moba_merge_fwd(void* out, float* lse, int32_t dtype, int32_t H, c
                                           static_cast<const uint16_t*>(part_o), part_lse, row_of);
   };
   const bool bf16 = dtype == MOBA_DTYPE_BF16;
-  if (info->kk <= 2) bf16 ? run(merge_fwd_kernel<true, 2>) : run(merge_fwd_kernel<false, 2>);
+  auto run_pairs = [&](auto kern) {
+    kern<<<row_grid((n + 1) / 2, kern), kRowWarps * 32, 0, st>>>(static_cast<uint16_t*>(out), lse, n, info->kk,
+                                                static_cast<const uint16_t*>(part_o), part_lse, row_of);
+  };
+  if (info->kk <= 2) bf16 ? run_pairs(merge_fwd_pair_kernel<true>) : run_pairs(merge_fwd_pair_kernel<false>);
   else bf16 ? run(merge_fwd_kernel<true, 4>) : run(merge_fwd_kernel<false, 4>);
   MOBA_CUDA_OK(cudaGetLastError());
   return 0;
