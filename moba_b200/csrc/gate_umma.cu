@@ -155,7 +155,16 @@ gate_topk_umma_kernel(const __grid_constant__ CUtensorMap map_q, int H, const fl
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
               const float s = __uint_as_float(r[c]);
-              if (cb + c < nb && s > best[KMAX - 1]) {
+              if constexpr (KMAX == 2) {
+                // two slots: the same insertion (strict >, the earlier candidate keeps a tie) as selects, no branch
+                const bool in = cb + c < nb;
+                const bool g0 = in && s > best[0], g1 = in && s > best[1];
+                const int ci = b0 + cb + c;
+                best[1] = g0 ? best[0] : (g1 ? s : best[1]);
+                bidx[1] = g0 ? bidx[0] : (g1 ? ci : bidx[1]);
+                best[0] = g0 ? s : best[0];
+                bidx[0] = g0 ? ci : bidx[0];
+              } else if (cb + c < nb && s > best[KMAX - 1]) {
                 best[KMAX - 1] = s;
                 bidx[KMAX - 1] = b0 + cb + c;
 #pragma unroll
@@ -562,6 +571,7 @@ int launch_gate_umma(const void* q, int32_t dtype, int32_t H, int64_t stride_s, 
     MOBA_CUDA_OK(cudaGetLastError());
     return 0;
   };
+  if (plan.kk <= 2) return bf16 ? run(gate_topk_umma_kernel<true, 2>) : run(gate_topk_umma_kernel<false, 2>);
   if (plan.kk <= 4) return bf16 ? run(gate_topk_umma_kernel<true, 4>) : run(gate_topk_umma_kernel<false, 4>);
   if (plan.kk <= 8) return bf16 ? run(gate_topk_umma_kernel<true, 8>) : run(gate_topk_umma_kernel<false, 8>);
   if (plan.kk <= 16) return bf16 ? run(gate_topk_umma_kernel<true, 16>) : run(gate_topk_umma_kernel<false, 16>);
