@@ -268,9 +268,23 @@ def cpu_sample(cfg_id, cfg, tokens, threads):
     return flops / secs / 1e12, secs, "numpy port of moba_attn_varlen_naive (baseline/_ref not installed) " + what, "port"
 
 
+def cpu_sample_bounded(cfg_id, cfg, tokens, threads, min_seconds=10.0, max_repeats=16):
+    """cpu_sample repeated until it has run for at least min_seconds (10-30 s of CPU work whatever the number of
+    host cores): the token count stays bounded by the dense function's O(tokens^2) memory, the duration by the
+    repeats. Returns (tflops over all repeats, total seconds, description, kind)."""
+    total, n = 0.0, 0
+    flops_s = 0.0
+    while n < max_repeats and (n == 0 or total < min_seconds):
+        tf, secs, desc, kind = cpu_sample(cfg_id, cfg, tokens, threads)
+        flops_s += tf * secs
+        total += secs
+        n += 1
+    return flops_s / total, total, desc + (f", run {n} times" if n > 1 else ""), kind
+
+
 def cpu_sample_tokens(cfg):
-    """Bounded sample: the dense reference function needs O(tokens^2) fp32 per head; 16384 tokens are ~10 s of work
-    on 16 host threads."""
+    """Bounded sample: the dense reference function needs O(tokens^2) fp32 per head (1 GB per [tokens, tokens]
+    tensor at 16384 tokens); cpu_sample_bounded repeats it up to the wanted duration."""
     return min(16384, sum(cfg["lens"]) if len(cfg["lens"]) == 1 else max(cfg["lens"]))
 
 
@@ -284,7 +298,7 @@ def run_reference_arm(args, cfg_id, cfg):
         cpu_sample(cfg_id, cfg, min(tokens, 4096), threads)
     vals, secs = [], []
     for _ in range(args.steps):
-        tf, s_, desc, kind = cpu_sample(cfg_id, cfg, tokens, threads)
+        tf, s_, desc, kind = cpu_sample_bounded(cfg_id, cfg, tokens, threads)
         vals.append(tf)
         secs.append(s_)
     value = sum(vals) / len(vals)
@@ -540,7 +554,7 @@ def run_ours(args, cfg_id, cfg):
         if args.no_cpu_baseline:
             cpu = None
         else:
-            tf, secs, desc, kind = cpu_sample(cfg_id, cfg, cpu_sample_tokens(cfg), threads)
+            tf, secs, desc, kind = cpu_sample_bounded(cfg_id, cfg, cpu_sample_tokens(cfg), threads)
             cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": desc,
                    "seconds": secs}
         line = {
