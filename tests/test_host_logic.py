@@ -210,3 +210,19 @@ def test_decode_branch_rejects_more_queries_than_keys():
     q, k = torch.randn(1, 2, 5, 16), torch.randn(1, 2, 3, 16)
     with pytest.raises(ValueError, match="kv_len >= q_len"):
         moba_layer(None, MoBAConfig(4, 2), M(), q, k, k)
+
+
+def test_host_numa_nodes_reads_sysfs():
+    """The NUMA nodes bench.py reports beside the copy rates: every node that has CPUs, with CPU ids as integers;
+    together they cover the CPUs this process may run on (an empty dict only where sysfs has no node directory)."""
+    import os
+
+    from moba_b200.host_io import host_numa_nodes
+
+    nodes = host_numa_nodes()
+    if not os.path.isdir("/sys/devices/system/node"):
+        assert nodes == {}
+        return
+    assert nodes and all(isinstance(n, int) and cpus and all(isinstance(c, int) for c in cpus)
+                         for n, cpus in nodes.items())
+    assert os.sched_getaffinity(0) <= set().union(*nodes.values())
